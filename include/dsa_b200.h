@@ -1,0 +1,101 @@
+/* C ABI of libdsa_b200.so: the sm_100a kernels of the DeepSeek Sparse Attention
+ * (DSA) hot path -- lightning-indexer logits, per-row top-k selection and sparse
+ * MLA -- behind plain pointers and sizes.
+ *
+ * The reference project (sparse_attn/DSA.py) has no native ABI: it reaches its
+ * GPU kernels through late-bound Python imports.  Each entry point below names
+ * the reference call site it stands in for.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its comment says "host".
+ *   - The caller owns all buffers (inputs, outputs, workspace, status word); the
+ *     library allocates nothing and keeps no pointer after the call returns.
+ *   - Calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL =
+ *     the default stream) and never synchronise.
+ *   - Return value: 0 on success, a negative DSA_ERR_* code otherwise; nothing is
+ *     launched on error and dsa_last_error_string() describes it.
+ *   - `status` (may be NULL) is one int32 in device memory, zeroed by the caller.
+ *     Kernels write a non-zero code there instead of faulting: 1 = an internal
+ *     bounded wait expired, 2 = an index or page id was out of range (the access
+ *     was skipped).  Read it after synchronising when you want to check.
+ */
+#ifndef DSA_B200_H_
+#define DSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSA_OK 0
+#define DSA_ERR_SHAPE (-1)     /* unsupported or inconsistent sizes */
+#define DSA_ERR_ALIGN (-2)     /* pointer or stride alignment */
+#define DSA_ERR_WORKSPACE (-3) /* workspace missing or too small */
+#define DSA_ERR_CUDA (-4)      /* a CUDA runtime / driver call failed */
+#define DSA_ERR_ARG (-5)       /* NULL pointer or bad flag */
+
+#define DSA_W_F32 0
+#define DSA_W_BF16 1
+
+/* Library version (major*10000 + minor*100 + patch). */
+int dsa_version(void);
+/* Message of the most recent error on the calling thread ("" if none). */
+const char* dsa_last_error_string(void);
+
+/* Lightning-indexer logits, contiguous keys.
+ *   logits[t, s] = k_scale[s] * sum_h w[t,h] * relu(q[t,h,:] . k[s,:])  for ks[t] <= s < ke[t].
+ * Stands in for deep_gemm.fp8_mqa_logits(q_fp8, (k_fp8, k_scale), w, ks, ke) as
+ * called at sparse_attn/DSA.py:343-345, 547-552, 654-659.
+ *   q_fp8   [T, H, D] e4m3, contiguous, 16-byte aligned
+ *   k_fp8   [S, D]    e4m3, contiguous, 16-byte aligned
+ *   k_scale [S] fp32;  w [T, H] fp32 (DSA_W_F32) or bf16 (DSA_W_BF16), q scale folded in
+ *   ks, ke  [T] int32 (ks may be NULL = 0)
+ *   logits  [T, ld_logits] fp32, ld_logits >= S
+ * Supported: H in {4,8,16,32,64} with D = 128, and H in {4,64} with D = 64.
+ * clean != 0 also writes -inf to every column outside the window (the library
+ * call's default); clean == 0 leaves columns that lie in fully masked 128-key
+ * tiles untouched, which is all dsa_topk_select needs. */
+int dsa_indexer_logits(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
+                       const int32_t* ks, const int32_t* ke, float* logits, int64_t ld_logits, int T, int S,
+                       int H, int D, int clean, int32_t* status, void* stream);
+
+/* Lightning-indexer logits for decode over a paged FP8 key cache: one query
+ * token per sequence.  No counterpart call in the reference (it has no cache,
+ * sparse_attn/DSA.py:475-477); same arithmetic as dsa_indexer_logits with
+ * ks = 0, ke = ctx_len[b] and key s of sequence b stored at physical row
+ * block_table[b, s/64]*64 + s%64.
+ *   q_fp8 [B, H, 128] e4m3; w [B, H]; kcache [num_pages*64, 128] e4m3;
+ *   kscale [num_pages*64] fp32; block_table [B, table_stride] int32;
+ *   ctx_len [B] int32; logits [B, ld_logits] fp32, ld_logits >= max_ctx.
+ * Columns >= ctx_len[b] inside a processed tile get -inf; beyond are untouched. */
+int dsa_indexer_logits_paged(const void* q_fp8, const void* w, int w_dtype, const void* kcache,
+                             const float* kscale, const int32_t* block_table, int64_t table_stride,
+                             const int32_t* ctx_len, float* logits, int64_t ld_logits, int B, int H, int D,
+                             int num_pages, int max_ctx, int32_t* status, void* stream);
+
+/* Per-row top-k by radix select.  Stands in for logits.topk(k).indices at
+ * sparse_attn/DSA.py:361, 567, 675-676.  Row t considers columns
+ * [ks[t], min(ke[t], S)) only (ks NULL = 0, ke NULL = S) and writes k int32
+ * column indices to out_idx[t, 0:k]: the indices of the k largest values,
+ * unsorted, ties at the k-th value going to the lower column; when fewer than k
+ * columns are in the window all of them are written followed by -1 padding.
+ * Output is bit-identical from run to run. */
+int dsa_topk_select(const float* logits, int64_t ld_logits, const int32_t* ks, const int32_t* ke, int T, int S,
+                    int k, int32_t* out_idx, void* stream);
+
+/* Indexer logits + top-k in one call (the whole of IndexerSimulator.logits_step,
+ * sparse_attn/DSA.py:336-362).  `workspace` holds the fp32 logits of one chunk
+ * of query rows; dsa_indexer_topk_workspace_bytes gives the size that does the
+ * whole call in one chunk, smaller workspaces (>= one 256-row chunk) make it
+ * loop. */
+size_t dsa_indexer_topk_workspace_bytes(int T, int S);
+int dsa_indexer_topk(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
+                     const int32_t* ks, const int32_t* ke, int T, int S, int H, int D, int k, int32_t* out_idx,
+                     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSA_B200_H_ */

@@ -1,0 +1,158 @@
+// extern "C" surface of libdsa_b200.so (declared in include/dsa_b200.h): argument
+// checks, error strings and the calls into the kernel launchers.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "dsa_host.h"
+
+namespace dsa {
+
+struct IndexerArgs;   // defined with the kernel
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(DSA_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+  return DSA_OK;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// launchers implemented next to their kernels
+int indexer_logits_contiguous(const void* q, const void* k, const float* k_scale, const void* w, int w_dtype,
+                              const int32_t* ks, const int32_t* ke, float* logits, int64_t ld, int T, int S,
+                              int H, int D, int clean, int32_t* status, cudaStream_t stream);
+int indexer_logits_paged(const void* q, const void* w, int w_dtype, const void* kcache, const float* kscale,
+                         const int32_t* block_table, int64_t table_stride, const int32_t* ctx_len, float* logits,
+                         int64_t ld, int B, int H, int D, int num_pages, int max_ctx, int32_t* status,
+                         cudaStream_t stream);
+int topk_select_launch(const float* logits, int64_t ld, const int32_t* ks, const int32_t* ke, int T, int S, int k,
+                       int32_t* out, cudaStream_t stream);
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace dsa
+
+using namespace dsa;
+
+extern "C" {
+
+int dsa_version(void) { return 100; }
+
+const char* dsa_last_error_string(void) { return g_err; }
+
+int dsa_indexer_logits(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
+                       const int32_t* ks, const int32_t* ke, float* logits, int64_t ld_logits, int T, int S,
+                       int H, int D, int clean, int32_t* status, void* stream) {
+  g_err[0] = 0;
+  if (T < 0 || S < 0) return set_error(DSA_ERR_SHAPE, "indexer_logits: negative size (T=%d, S=%d)", T, S);
+  if (T == 0 || S == 0) return DSA_OK;
+  if (!q_fp8 || !k_fp8 || !k_scale || !w || !ke || !logits)
+    return set_error(DSA_ERR_ARG, "indexer_logits: NULL pointer argument");
+  if (w_dtype != DSA_W_F32 && w_dtype != DSA_W_BF16)
+    return set_error(DSA_ERR_ARG, "indexer_logits: w_dtype must be DSA_W_F32 or DSA_W_BF16");
+  if (ld_logits < S) return set_error(DSA_ERR_SHAPE, "indexer_logits: ld_logits (%lld) < S (%d)", (long long)ld_logits, S);
+  if (!aligned16(q_fp8) || !aligned16(k_fp8))
+    return set_error(DSA_ERR_ALIGN, "indexer_logits: q_fp8 and k_fp8 must be 16-byte aligned");
+  if ((int64_t)T * H > 0x7fffffffLL) return set_error(DSA_ERR_SHAPE, "indexer_logits: T*H exceeds 2^31");
+  return indexer_logits_contiguous(q_fp8, k_fp8, k_scale, w, w_dtype, ks, ke, logits, ld_logits, T, S, H, D, clean,
+                                   status, static_cast<cudaStream_t>(stream));
+}
+
+int dsa_indexer_logits_paged(const void* q_fp8, const void* w, int w_dtype, const void* kcache,
+                             const float* kscale, const int32_t* block_table, int64_t table_stride,
+                             const int32_t* ctx_len, float* logits, int64_t ld_logits, int B, int H, int D,
+                             int num_pages, int max_ctx, int32_t* status, void* stream) {
+  g_err[0] = 0;
+  if (B < 0 || max_ctx < 0 || num_pages < 0)
+    return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: negative size");
+  if (B == 0 || max_ctx == 0) return DSA_OK;
+  if (!q_fp8 || !w || !kcache || !kscale || !block_table || !ctx_len || !logits)
+    return set_error(DSA_ERR_ARG, "indexer_logits_paged: NULL pointer argument");
+  if (w_dtype != DSA_W_F32 && w_dtype != DSA_W_BF16)
+    return set_error(DSA_ERR_ARG, "indexer_logits_paged: bad w_dtype");
+  if (ld_logits < max_ctx) return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: ld_logits < max_ctx");
+  if (table_stride * 64 < max_ctx)
+    return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: block table row (%lld pages) shorter than max_ctx %d",
+                     (long long)table_stride, max_ctx);
+  if (!aligned16(q_fp8) || !aligned16(kcache))
+    return set_error(DSA_ERR_ALIGN, "indexer_logits_paged: q_fp8 and kcache must be 16-byte aligned");
+  if ((int64_t)num_pages * 64 > 0x7fffffffLL) return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: cache too large");
+  return indexer_logits_paged(q_fp8, w, w_dtype, kcache, kscale, block_table, table_stride, ctx_len, logits,
+                              ld_logits, B, H, D, num_pages, max_ctx, status, static_cast<cudaStream_t>(stream));
+}
+
+int dsa_topk_select(const float* logits, int64_t ld_logits, const int32_t* ks, const int32_t* ke, int T, int S,
+                    int k, int32_t* out_idx, void* stream) {
+  g_err[0] = 0;
+  if (T < 0 || S < 0 || k < 0) return set_error(DSA_ERR_SHAPE, "topk_select: negative size");
+  if (T == 0 || k == 0) return DSA_OK;
+  if (!logits || !out_idx) return set_error(DSA_ERR_ARG, "topk_select: NULL pointer argument");
+  if (ld_logits < S) return set_error(DSA_ERR_SHAPE, "topk_select: ld_logits < S");
+  if (k > 65535) return set_error(DSA_ERR_SHAPE, "topk_select: k (%d) exceeds 65535", k);
+  return topk_select_launch(logits, ld_logits, ks, ke, T, S, k, out_idx, static_cast<cudaStream_t>(stream));
+}
+
+static const int kMinChunkRows = 256;
+
+static int64_t logits_ld(int S) { return ((int64_t)S + 3) & ~int64_t(3); }
+
+size_t dsa_indexer_topk_workspace_bytes(int T, int S) {
+  if (T <= 0 || S <= 0) return 0;
+  return (size_t)T * (size_t)logits_ld(S) * sizeof(float);
+}
+
+int dsa_indexer_topk(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
+                     const int32_t* ks, const int32_t* ke, int T, int S, int H, int D, int k, int32_t* out_idx,
+                     void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  g_err[0] = 0;
+  if (T < 0 || S < 0 || k < 0) return set_error(DSA_ERR_SHAPE, "indexer_topk: negative size");
+  if (T == 0 || k == 0) return DSA_OK;
+  if (S == 0) return set_error(DSA_ERR_SHAPE, "indexer_topk: S = 0 with k > 0");
+  if (!out_idx || !ke) return set_error(DSA_ERR_ARG, "indexer_topk: NULL pointer argument");
+  const int64_t ld = logits_ld(S);
+  const size_t row_bytes = (size_t)ld * sizeof(float);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return set_error(DSA_ERR_WORKSPACE, "indexer_topk: workspace missing or not 16-byte aligned");
+  int64_t rows = (int64_t)(workspace_bytes / row_bytes);
+  const int min_rows = T < kMinChunkRows ? T : kMinChunkRows;
+  if (rows < min_rows)
+    return set_error(DSA_ERR_WORKSPACE, "indexer_topk: workspace %zu B holds %lld rows, need >= %d (%zu B)",
+                     workspace_bytes, (long long)rows, min_rows, (size_t)min_rows * row_bytes);
+  if (rows > T) rows = T;
+  if (rows < T) rows &= ~int64_t(kMinChunkRows - 1);   // whole query groups per chunk
+  float* logits = static_cast<float*>(workspace);
+  const size_t w_elt = w_dtype == DSA_W_BF16 ? 2 : 4;
+  for (int64_t r0 = 0; r0 < T; r0 += rows) {
+    const int n = (int)((T - r0 < rows) ? T - r0 : rows);
+    int rc = dsa_indexer_logits(static_cast<const uint8_t*>(q_fp8) + (size_t)r0 * H * D, k_fp8, k_scale,
+                                static_cast<const uint8_t*>(w) + (size_t)r0 * H * w_elt, w_dtype,
+                                ks ? ks + r0 : nullptr, ke + r0, logits, ld, n, S, H, D, /*clean=*/0, status, stream);
+    if (rc) return rc;
+    rc = dsa_topk_select(logits, ld, ks ? ks + r0 : nullptr, ke + r0, n, S, k, out_idx + (size_t)r0 * k, stream);
+    if (rc) return rc;
+  }
+  return DSA_OK;
+}
+
+}  // extern "C"

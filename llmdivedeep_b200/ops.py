@@ -1,0 +1,182 @@
+"""Torch-facing wrappers over the C ABI: tensors in, tensors out, current stream.
+
+Every function checks dtypes/shapes, passes raw device pointers to
+libdsa_b200.so and raises ``DsaError`` when the library refuses the call.
+Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import DsaError, check
+
+FP8 = torch.float8_e4m3fn
+_status = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise DsaError("libdsa_b200 kernels take CUDA tensors only (there is no CPU path)")
+
+
+def status_word(device) -> torch.Tensor:
+    """The per-device int32 the kernels report soft errors into."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Synchronise and raise if a kernel flagged a soft error since the last check."""
+    w = status_word(device)
+    v = int(w.item())
+    if v:
+        w.zero_()
+        what = {1: "a bounded wait inside a kernel expired", 2: "an index or page id was out of range"}.get(v, "?")
+        raise DsaError(f"device status {v}: {what}")
+
+
+def _w_dtype(w: torch.Tensor) -> int:
+    if w.dtype == torch.float32:
+        return 0
+    if w.dtype == torch.bfloat16:
+        return 1
+    raise DsaError(f"head weights must be fp32 or bf16, got {w.dtype}")
+
+
+def _as_i32(t: Optional[torch.Tensor], n: int, name: str) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.int32 or t.numel() != n or not t.is_contiguous():
+        raise DsaError(f"{name} must be a contiguous int32 tensor of {n} elements")
+    return t
+
+
+def fp8_mqa_logits(q_fp8, kv, weights, ks, ke, clean_logits: bool = True,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Drop-in for ``deep_gemm.fp8_mqa_logits(q_fp8, (k_fp8, k_scale), w, ks, ke)``
+    as the reference calls it (sparse_attn/DSA.py:343-345).  Returns fp32 [T, S]."""
+    k_fp8, k_scale = kv
+    _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke)
+    if q_fp8.dtype != FP8 or k_fp8.dtype != FP8:
+        raise DsaError("q and k must be float8_e4m3fn")
+    if q_fp8.dim() != 3 or k_fp8.dim() != 2 or q_fp8.shape[2] != k_fp8.shape[1]:
+        raise DsaError(f"bad shapes q {tuple(q_fp8.shape)} k {tuple(k_fp8.shape)}")
+    T, H, D = q_fp8.shape
+    S = k_fp8.shape[0]
+    q_fp8, k_fp8 = q_fp8.contiguous(), k_fp8.contiguous()
+    k_scale = k_scale.reshape(-1).to(torch.float32).contiguous()
+    weights = weights.contiguous()
+    if k_scale.numel() != S or tuple(weights.shape) != (T, H):
+        raise DsaError("k_scale must have S entries and weights must be [T, H]")
+    ks = _as_i32(ks, T, "ks")
+    ke = _as_i32(ke, T, "ke")
+    ld = (S + 3) // 4 * 4
+    if out is None:
+        out = torch.empty(T, ld, dtype=torch.float32, device=q_fp8.device)
+    elif out.dtype != torch.float32 or out.dim() != 2 or out.shape[0] < T or out.stride(1) != 1 or out.stride(0) < S:
+        raise DsaError("out must be fp32 [>=T, >=S] with unit column stride")
+    else:
+        ld = out.stride(0)
+    lib = _lib.load()
+    check(lib.dsa_indexer_logits(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
+                                 _ptr(ks), _ptr(ke), _ptr(out), ld, T, S, H, D, int(bool(clean_logits)),
+                                 _ptr(status_word(q_fp8.device)), _stream()))
+    return out[:T, :S]
+
+
+def fp8_paged_mqa_logits(q_fp8, weights, kcache, kscale, block_table, ctx_len, max_ctx: int,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode indexer over the paged FP8 key cache.  q_fp8 [B,H,128], weights [B,H],
+    kcache [num_pages*64,128] e4m3, kscale [num_pages*64] fp32, block_table [B,P] int32,
+    ctx_len [B] int32.  Returns fp32 [B, max_ctx]; columns >= ctx_len[b] inside a
+    processed 128-key tile hold -inf, columns beyond are uninitialised."""
+    _need_cuda(q_fp8, weights, kcache, kscale, block_table, ctx_len)
+    B, H, D = q_fp8.shape
+    if kcache.dtype != FP8 or q_fp8.dtype != FP8 or kcache.dim() != 2 or kcache.shape[1] != D:
+        raise DsaError("kcache must be float8_e4m3fn [num_pages*64, D]")
+    if kcache.shape[0] % 64:
+        raise DsaError("kcache rows must be a multiple of the 64-token page")
+    block_table = block_table.contiguous()
+    if block_table.dtype != torch.int32 or block_table.shape[0] != B:
+        raise DsaError("block_table must be int32 [B, pages]")
+    ctx_len = _as_i32(ctx_len, B, "ctx_len")
+    q_fp8, kcache, weights = q_fp8.contiguous(), kcache.contiguous(), weights.contiguous()
+    kscale = kscale.reshape(-1).to(torch.float32).contiguous()
+    ld = (max_ctx + 3) // 4 * 4
+    if out is None:
+        out = torch.empty(B, ld, dtype=torch.float32, device=q_fp8.device)
+    else:
+        ld = out.stride(0)
+    lib = _lib.load()
+    check(lib.dsa_indexer_logits_paged(_ptr(q_fp8), _ptr(weights), _w_dtype(weights), _ptr(kcache), _ptr(kscale),
+                                       _ptr(block_table), block_table.stride(0), _ptr(ctx_len), _ptr(out), ld,
+                                       B, H, D, kcache.shape[0] // 64, max_ctx,
+                                       _ptr(status_word(q_fp8.device)), _stream()))
+    return out[:B, :max_ctx]
+
+
+def topk_select(logits: torch.Tensor, k: int, ks=None, ke=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Indices (int32, unsorted) of the k largest entries of each row's window
+    [ks, ke); -1 padding when the window holds fewer than k columns."""
+    _need_cuda(logits, ks, ke)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise DsaError("logits must be fp32 [T, S] with unit column stride")
+    T, S = logits.shape
+    ks = _as_i32(ks, T, "ks")
+    ke = _as_i32(ke, T, "ke")
+    if out is None:
+        out = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    lib = _lib.load()
+    check(lib.dsa_topk_select(_ptr(logits), logits.stride(0) if T > 1 else max(S, logits.stride(0)), _ptr(ks),
+                              _ptr(ke), T, S, k, _ptr(out), _stream()))
+    return out
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    w = _workspaces.get(key)
+    if w is None or w.numel() < nbytes:
+        _workspaces[key] = w = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{key}")
+    return w
+
+
+def indexer_topk(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, workspace: Optional[torch.Tensor] = None,
+                 max_workspace_bytes: int = 8 << 30, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Indexer logits + top-k (IndexerSimulator.logits_step, sparse_attn/DSA.py:336-362)
+    in one library call.  Returns int32 [T, min(k, S)]."""
+    _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke)
+    T, H, D = q_fp8.shape
+    S = k_fp8.shape[0]
+    k = min(k, S)
+    q_fp8, k_fp8, weights = q_fp8.contiguous(), k_fp8.contiguous(), weights.contiguous()
+    k_scale = k_scale.reshape(-1).to(torch.float32).contiguous()
+    ks = _as_i32(ks, T, "ks")
+    ke = _as_i32(ke, T, "ke")
+    lib = _lib.load()
+    if workspace is None:
+        full = lib.dsa_indexer_topk_workspace_bytes(T, S)
+        row = full // max(T, 1)
+        workspace = _workspace(q_fp8.device, min(full, max(max_workspace_bytes, 256 * row)))
+    if out is None:
+        out = torch.empty(T, k, dtype=torch.int32, device=q_fp8.device)
+    check(lib.dsa_indexer_topk(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
+                               _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out), _ptr(workspace), workspace.numel(),
+                               _ptr(status_word(q_fp8.device)), _stream()))
+    return out
