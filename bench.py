@@ -164,6 +164,7 @@ def measured_peaks():
 
 
 def main():
+    global T_ROWS, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -173,7 +174,6 @@ def main():
     ap.add_argument("--rows", type=int, default=T_ROWS,
                     help="query rows per step; anything but 4096 is a reduced case for profiler captures, not a bench value")
     args = ap.parse_args()
-    global T_ROWS, WORKLOAD
     if args.rows != T_ROWS:
         T_ROWS = args.rows
         WORKLOAD = f"REDUCED profiling case ({T_ROWS} query rows, pos {S_KEYS - T_ROWS}-{S_KEYS - 1}) of: " + WORKLOAD

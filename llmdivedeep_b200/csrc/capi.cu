@@ -75,6 +75,9 @@ int dsa_indexer_logits(const void* q_fp8, const void* k_fp8, const float* k_scal
   if (!aligned16(q_fp8) || !aligned16(k_fp8))
     return set_error(DSA_ERR_ALIGN, "indexer_logits: q_fp8 and k_fp8 must be 16-byte aligned");
   if ((int64_t)T * H > 0x7fffffffLL) return set_error(DSA_ERR_SHAPE, "indexer_logits: T*H exceeds 2^31");
+  if (ld_logits * 64 > 0x7fffffffLL)
+    return set_error(DSA_ERR_SHAPE, "indexer_logits: ld_logits (%lld) too large (64 * ld must stay below 2^31)",
+                     (long long)ld_logits);
   return indexer_logits_contiguous(q_fp8, k_fp8, k_scale, w, w_dtype, ks, ke, logits, ld_logits, T, S, H, D, clean,
                                    status, static_cast<cudaStream_t>(stream));
 }
@@ -92,6 +95,7 @@ int dsa_indexer_logits_paged(const void* q_fp8, const void* w, int w_dtype, cons
   if (w_dtype != DSA_W_F32 && w_dtype != DSA_W_BF16)
     return set_error(DSA_ERR_ARG, "indexer_logits_paged: bad w_dtype");
   if (ld_logits < max_ctx) return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: ld_logits < max_ctx");
+  if (ld_logits * 64 > 0x7fffffffLL) return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: ld_logits too large");
   if (table_stride * 64 < max_ctx)
     return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: block table row (%lld pages) shorter than max_ctx %d",
                      (long long)table_stride, max_ctx);

@@ -6,26 +6,32 @@
 // One persistent CTA per SM.  A tile is 128 keys (the MMA M dimension, one TMEM
 // lane per key) by N = NQ*H (token, head) pairs (the MMA N dimension, one TMEM
 // column per pair).  FP8 e4m3 operands are fetched by TMA with the 128-byte (or
-// 64-byte) swizzle the UMMA descriptors expect, tcgen05.mma accumulates in fp32
-// in tensor memory, and two epilogue warpgroups drain alternate accumulator
-// stages: every thread owns one key, walks the columns of its lane, applies
-// ReLU, multiplies by the head weight (broadcast from shared memory) and sums
-// the H heads of each token -- a purely thread-local reduction.  The sum order
-// is fixed (even heads ascending, odd heads ascending, then even + odd), so
-// results are bit-identical from run to run.
+// 64-byte) swizzle the UMMA descriptors expect and tcgen05.mma accumulates in
+// fp32 in tensor memory.  A work unit is a block of QB query groups against a
+// chunk of 64 key tiles: every key tile fetched from L2 is multiplied with all
+// QB resident query tiles, which divides the L2 -> shared-memory key traffic by
+// QB (at QB = 1 that traffic, not the tensor pipe, bounds the kernel).
 //
-// Roles: warp 0 lane 0 = TMA producer, warp 1 lane 0 = MMA issuer (warp 1 owns
-// the TMEM allocation), warps 4-7 and 8-11 = epilogue warpgroups 0 and 1.
+// Epilogue warpgroups drain alternate accumulator stages: every thread owns one
+// key, walks the columns of its lane, applies ReLU, multiplies by the head
+// weight (broadcast from shared memory) and sums the H heads of each token -- a
+// purely thread-local reduction with a fixed order (head pair p of a token goes
+// to chain p mod 2, score = (chain0.even + chain0.odd) + (chain1.even +
+// chain1.odd)), so results are bit-identical from run to run.
+//
+// Roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation),
+// warp 2 = stages head weights and windows of the next unit, warps 4.. =
+// epilogue.  All waits are bounded (see dsa_common.cuh).
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math_constants.h>
+#include <stdlib.h>
 
 #include "dsa_common.cuh"
 #include "dsa_host.h"
 
 namespace dsa {
 
-constexpr int kIdxThreads = 384;
 constexpr int kTileKeys = 128;
 constexpr int kChunkTiles = 64;        // key tiles per work unit
 constexpr int kPageTokens = 64;
@@ -46,30 +52,39 @@ struct IndexerArgs {
   int* status;
 };
 
-template <int H, int D, int NQ, bool PAGED>
+template <int H, int D, int NQ, bool PAGED, int QB, int EPI>
 struct IdxCfg {
-  static constexpr int N = H * NQ;
+  static constexpr int N = H * NQ;                       // accumulator columns = (token, head) pairs
+  static constexpr int NTOK = NQ * QB;                   // query tokens per work unit
   static constexpr int KSTEPS = D / 32;
   static constexpr int K_TILE_BYTES = kTileKeys * D;
   static constexpr int Q_TILE_BYTES = N * D;
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = (QB == 1) ? 6 : 4;
   static constexpr int TMEM_COLS = (2 * N < 32) ? 32 : 2 * N;
   static constexpr uint64_t SWZ = (D == 128) ? kSwz128 : kSwz64;
   static constexpr uint32_t SBO = 8 * D;                 // 8 rows of D bytes
-  static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * K_TILE_BYTES + 2 * Q_TILE_BYTES +
-                                    8 * N * 4 + 16 * NQ * 4 + 256;
+  static constexpr int EPI_WARPS = EPI * 4;
+  static constexpr int THREADS = 128 + EPI * 128;
+  static constexpr int SPLIT = EPI / 2;                  // warpgroups sharing one accumulator stage
+  static constexpr int COLS_PER_WG = N / SPLIT;
+  static constexpr int CH = 16;                          // columns per TMEM load
+  static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * K_TILE_BYTES + 2 * QB * Q_TILE_BYTES +
+                                    2 * QB * N * 4 + 2 * NTOK * 8 + 256;
+  static_assert(EPI == 2 || EPI == 4, "two or four epilogue warpgroups");
   static_assert(N % 16 == 0 && N >= 16 && N <= 256, "MMA N out of range");
+  static_assert(COLS_PER_WG % H == 0 && COLS_PER_WG % CH == 0, "a warpgroup must own whole tokens");
   static_assert(D == 64 || D == 128, "head dim must be 64 or 128");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
-// [min ks, max ke) over the tokens of group g, computed by one full warp.
-template <int NQ, bool PAGED>
-__device__ __forceinline__ void group_window(const IndexerArgs& a, int g, int& lo, int& hi) {
+// [min ks, max ke) over tokens [t0, t0 + ntok), computed by one full warp.
+template <bool PAGED>
+__device__ __forceinline__ void token_window(const IndexerArgs& a, int t0, int ntok, int& lo, int& hi) {
   const int lane = threadIdx.x & 31;
   int mn = 0x7fffffff, mx = 0;
-  for (int j = lane; j < NQ; j += 32) {
-    const int t = g * NQ + j;
+  for (int j = lane; j < ntok; j += 32) {
+    const int t = t0 + j;
     if (t < a.T) {
       const int s0 = (!PAGED && a.ks) ? a.ks[t] : 0;
       const int s1 = a.ke[t];
@@ -86,39 +101,119 @@ __device__ __forceinline__ void group_window(const IndexerArgs& a, int g, int& l
   hi = mx;
 }
 
-// key-tile range of work unit u (same answer in every role)
-template <int NQ, bool PAGED>
-__device__ __forceinline__ bool unit_tiles(const IndexerArgs& a, int u, int n_groups, int& g, int& t_lo,
-                                           int& t_hi) {
-  const int c = u / n_groups;
-  g = u - c * n_groups;
+// Work unit u -> query block qb, key-tile range [t_lo, t_hi), groups in the block nb.
+// Called by a full warp; every role gets the same answer.
+template <int NQ, int QB, bool PAGED>
+__device__ __forceinline__ bool unit_tiles(const IndexerArgs& a, int u, int n_qblocks, int n_groups, int& qb,
+                                           int& nb, int& t_lo, int& t_hi) {
+  const int c = u / n_qblocks;
+  qb = u - c * n_qblocks;
+  nb = min(QB, n_groups - qb * QB);
   int lo, hi;
-  group_window<NQ, PAGED>(a, g, lo, hi);
+  token_window<PAGED>(a, qb * QB * NQ, nb * NQ, lo, hi);
   if (hi <= lo) return false;
   t_lo = max(c * kChunkTiles, lo / kTileKeys);
   t_hi = min((c + 1) * kChunkTiles, (hi + kTileKeys - 1) / kTileKeys);
   return t_lo < t_hi;
 }
 
-template <int H, int D, int NQ, bool PAGED>
-__global__ void __launch_bounds__(kIdxThreads, 1)
+// One thread = one key.  Walks NCOLS accumulator columns starting at column COL0 of
+// its TMEM lane.  Weights of chunk c+1 and its TMEM load are both requested before
+// the math of chunk c, in that order: shared-memory loads queue behind a TMEM load
+// issued earlier by the same warp, so the weights must go first to overlap.
+#ifdef DSA_IDX_NOWLDS   // experiment: no shared-memory weight loads
+#define DSA_WLOAD(p) make_float4(kscale, kscale * 0.5f, kscale * 0.25f, kscale * 2.f)
+#else
+#define DSA_WLOAD(p) (*reinterpret_cast<const float4*>(p))
+#endif
+
+template <int H, int NQ, int CH, int COL0, int NCOLS>
+__device__ __forceinline__ void drain_columns(uint32_t t_lane, const float* __restrict__ w_s,
+                                              const int2* __restrict__ win_s, float kscale, int s, bool s_ok,
+                                              int n_tok, float* __restrict__ grp_base, uint32_t ld) {
+  constexpr int NCH = 2;
+  uint32_t v[2][CH];
+  float4 wv[2][CH / 4];
+  uint64_t chain[NCH];
+#pragma unroll
+  for (int i = 0; i < CH / 4; ++i) wv[0][i] = DSA_WLOAD(w_s + COL0 + 4 * i);
+  tmem_ld16(t_lane + COL0, v[0]);
+#pragma unroll
+  for (int c = 0; c < NCOLS; c += CH) {
+    const int cur = (c / CH) & 1;
+    tmem_wait_ld();
+    if (c + CH < NCOLS) {
+#pragma unroll
+      for (int i = 0; i < CH / 4; ++i)
+        wv[cur ^ 1][i] = DSA_WLOAD(w_s + COL0 + c + CH + 4 * i);
+      tmem_ld16(t_lane + COL0 + c + CH, v[cur ^ 1]);
+    }
+#pragma unroll
+    for (int i = 0; i < CH; i += 4) {
+      const int col = COL0 + c + i;                       // multiple of 4
+      const float4 w4 = wv[cur][i / 4];
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        const int cp = col + 2 * p;                       // first column of this pair
+        const int hp = (cp % H) / 2;                      // pair index inside the token
+        const float d0 = fmaxf(__uint_as_float(v[cur][i + 2 * p]), 0.f);
+        const float d1 = fmaxf(__uint_as_float(v[cur][i + 2 * p + 1]), 0.f);
+        const uint64_t wp = p == 0 ? pack_f32x2(w4.x, w4.y) : pack_f32x2(w4.z, w4.w);
+        if (hp < NCH) chain[hp % NCH] = 0;                // first use of the chain in this token
+        chain[hp % NCH] = fma_f32x2(pack_f32x2(d0, d1), wp, chain[hp % NCH]);
+        if (cp % H == H - 2) {                            // last pair of the token
+          float score = 0.f;
+#pragma unroll
+          for (int q = 0; q < NCH; ++q) {
+            float e, o;
+            unpack_f32x2(chain[q], e, o);
+            score += e + o;
+          }
+          const int j = cp / H;                           // token within the group
+          const int2 win = win_s[j];                      // (ks, ke - ks)
+          const bool in = static_cast<uint32_t>(s - win.x) < static_cast<uint32_t>(win.y);
+          if (s_ok && j < n_tok) grp_base[static_cast<uint32_t>(j) * ld + static_cast<uint32_t>(s)] =
+              in ? score * kscale : -CUDART_INF_F;
+        }
+      }
+    }
+  }
+}
+
+#ifdef DSA_IDX_PROFILE
+__device__ long long g_prof[148 * 16];
+#define PROF_T0() long long _pt = clock64()
+#define PROF_ADD(slot) do { long long _n = clock64(); _acc[slot] += _n - _pt; _pt = _n; } while (0)
+#define PROF_DECL() long long _acc[4] = {0, 0, 0, 0}
+#define PROF_STORE(base) do { if (lane == 0) for (int _i = 0; _i < 4; ++_i) g_prof[blockIdx.x * 16 + (base) + _i] = _acc[_i]; } while (0)
+#else
+#define PROF_T0()
+#define PROF_ADD(slot)
+#define PROF_DECL()
+#define PROF_STORE(base)
+#endif
+
+template <int H, int D, int NQ, bool PAGED, int QB, int EPI>
+__global__ void __launch_bounds__(IdxCfg<H, D, NQ, PAGED, QB, EPI>::THREADS, 1)
 indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                      const IndexerArgs a, const int n_groups, const int n_units) {
-  using C = IdxCfg<H, D, NQ, PAGED>;
+                      const IndexerArgs a, const int n_groups, const int n_qblocks, const int n_units) {
+  using C = IdxCfg<H, D, NQ, PAGED, QB, EPI>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* k_s = smem;                                        // STAGES x [128 keys x D]
-  uint8_t* q_s = k_s + C::STAGES * C::K_TILE_BYTES;           // 2 x [N rows x D]
-  float* w_s = reinterpret_cast<float*>(q_s + 2 * C::Q_TILE_BYTES);   // 8 warps x N (private copies)
-  int* win_s = reinterpret_cast<int*>(w_s + 8 * C::N);        // 8 warps x (ks[NQ], ke[NQ])
-  uint64_t* bars = reinterpret_cast<uint64_t*>(win_s + 16 * NQ);
+  uint8_t* q_s = k_s + C::STAGES * C::K_TILE_BYTES;           // 2 x QB x [N rows x D]
+  float* w_s = reinterpret_cast<float*>(q_s + 2 * QB * C::Q_TILE_BYTES);   // 2 x QB x N head weights
+  int2* win_s = reinterpret_cast<int2*>(w_s + 2 * QB * C::N);              // 2 x NTOK (ks, ke - ks)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(win_s + 2 * C::NTOK);
   uint64_t* k_full = bars;                  // [STAGES]
   uint64_t* k_empty = k_full + C::STAGES;   // [STAGES]
   uint64_t* q_full = k_empty + C::STAGES;   // [2]
   uint64_t* q_empty = q_full + 2;           // [2]
   uint64_t* acc_full = q_empty + 2;         // [2]
   uint64_t* acc_empty = acc_full + 2;       // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* w_full = acc_empty + 2;         // [2]
+  uint64_t* w_empty = w_full + 2;           // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -133,7 +228,9 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 4);       // one arrive per epilogue warp
+      mbar_init(&acc_empty[i], 4 * C::SPLIT);   // one arrive per epilogue warp draining the stage
+      mbar_init(&w_full[i], 1);
+      mbar_init(&w_empty[i], C::EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -153,56 +250,56 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     // ------------------------------ TMA producer ------------------------------
     uint32_t it = 0, nu = 0;
     for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
-      int g, t_lo, t_hi;
-      if (!unit_tiles<NQ, PAGED>(a, u, n_groups, g, t_lo, t_hi)) continue;
+      int qb, nb, t_lo, t_hi;
+      if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
       const int qs = nu & 1;
       bool ok = true;
       if (lane == 0) {
         ok = mbar_wait(&q_empty[qs], ((nu >> 1) & 1) ^ 1, abort_flag, a.status);
         if (ok) {
-          mbar_expect_tx(&q_full[qs], C::Q_TILE_BYTES);
-          tma_load_2d(q_s + qs * C::Q_TILE_BYTES, &tmap_q, 0, g * C::N, &q_full[qs]);
+          mbar_expect_tx(&q_full[qs], nb * C::Q_TILE_BYTES);
+          for (int b = 0; b < nb; ++b)
+            tma_load_2d(q_s + (qs * QB + b) * C::Q_TILE_BYTES, &tmap_q, 0, (qb * QB + b) * C::N, &q_full[qs]);
+        }
+        for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
+          const int st = it % C::STAGES;
+          ok = mbar_wait(&k_empty[st], ((it / C::STAGES) & 1) ^ 1, abort_flag, a.status);
+          if (!ok) break;
+          uint8_t* dst = k_s + st * C::K_TILE_BYTES;
+          if constexpr (!PAGED) {
+            mbar_expect_tx(&k_full[st], C::K_TILE_BYTES);
+            tma_load_2d(dst, &tmap_k, 0, kt * kTileKeys, &k_full[st]);
+          } else {
+            // two 64-token pages per tile; a missing or out-of-range page is skipped
+            const int n_pages = (min(a.ke[qb], a.S) + kPageTokens - 1) / kPageTokens;
+            int rows[2];
+            uint32_t bytes = 0;
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+              const int page = kt * 2 + p;
+              rows[p] = -1;
+              if (page < n_pages) {
+                const int phys = a.block_table[(int64_t)qb * a.table_stride + page];
+                if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows) {
+                  rows[p] = phys * kPageTokens;
+                  bytes += C::K_TILE_BYTES / 2;
+                } else if (a.status) {
+                  atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+                }
+              }
+            }
+            if (bytes) {
+              mbar_expect_tx(&k_full[st], bytes);
+#pragma unroll
+              for (int p = 0; p < 2; ++p)
+                if (rows[p] >= 0) tma_load_2d(dst + p * (C::K_TILE_BYTES / 2), &tmap_k, 0, rows[p], &k_full[st]);
+            } else {
+              mbar_arrive(&k_full[st]);
+            }
+          }
         }
       }
       ++nu;
-      for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
-        if (lane != 0) continue;
-        const int st = it % C::STAGES;
-        ok = mbar_wait(&k_empty[st], ((it / C::STAGES) & 1) ^ 1, abort_flag, a.status);
-        if (!ok) break;
-        uint8_t* dst = k_s + st * C::K_TILE_BYTES;
-        if constexpr (!PAGED) {
-          mbar_expect_tx(&k_full[st], C::K_TILE_BYTES);
-          tma_load_2d(dst, &tmap_k, 0, kt * kTileKeys, &k_full[st]);
-        } else {
-          // two 64-token pages per tile; a missing or out-of-range page is skipped
-          const int n_pages = (min(a.ke[g], a.S) + kPageTokens - 1) / kPageTokens;
-          int rows[2];
-          uint32_t bytes = 0;
-#pragma unroll
-          for (int p = 0; p < 2; ++p) {
-            const int page = kt * 2 + p;
-            rows[p] = -1;
-            if (page < n_pages) {
-              const int phys = a.block_table[(int64_t)g * a.table_stride + page];
-              if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows) {
-                rows[p] = phys * kPageTokens;
-                bytes += C::K_TILE_BYTES / 2;
-              } else if (a.status) {
-                atomicCAS(a.status, kStatusOk, kStatusBadIndex);
-              }
-            }
-          }
-          if (bytes) {
-            mbar_expect_tx(&k_full[st], bytes);
-#pragma unroll
-            for (int p = 0; p < 2; ++p)
-              if (rows[p] >= 0) tma_load_2d(dst + p * (C::K_TILE_BYTES / 2), &tmap_k, 0, rows[p], &k_full[st]);
-          } else {
-            mbar_arrive(&k_full[st]);
-          }
-        }
-      }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       it = __shfl_sync(0xffffffffu, it, 0);
       if (!ok) break;
@@ -217,130 +314,159 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     constexpr uint32_t idesc = umma_idesc(0, 0, 0, 0, kTileKeys, C::N);
-    uint32_t it = 0, nu = 0;
+    uint32_t it = 0, it2 = 0, nu = 0;
+    PROF_DECL();
+    PROF_T0();
     for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
-      int g, t_lo, t_hi;
-      if (!unit_tiles<NQ, PAGED>(a, u, n_groups, g, t_lo, t_hi)) continue;
+      int qb, nb, t_lo, t_hi;
+      if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
       const int qs = nu & 1;
       bool ok = true;
       if (lane == 0) {
+        PROF_ADD(3);
         ok = mbar_wait(&q_full[qs], (nu >> 1) & 1, abort_flag, a.status);
-        const uint64_t qdesc = umma_smem_desc(smem_u32(q_s + qs * C::Q_TILE_BYTES), 16, C::SBO, C::SWZ);
+        PROF_ADD(0);
         for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
           const int st = it % C::STAGES;
-          const int acc = it & 1;
-          ok = mbar_wait(&k_full[st], (it / C::STAGES) & 1, abort_flag, a.status) &&
-               mbar_wait(&acc_empty[acc], ((it >> 1) & 1) ^ 1, abort_flag, a.status);
-          if (!ok) break;
-          tc_fence_after();
+          ok = mbar_wait(&k_full[st], (it / C::STAGES) & 1, abort_flag, a.status);
+          PROF_ADD(1);
           const uint64_t kdesc = umma_smem_desc(smem_u32(k_s + st * C::K_TILE_BYTES), 16, C::SBO, C::SWZ);
+          for (int b = 0; b < nb && ok; ++b, ++it2) {
+            const int acc = it2 & 1;
+            ok = mbar_wait(&acc_empty[acc], ((it2 >> 1) & 1) ^ 1, abort_flag, a.status);
+            PROF_ADD(2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t qdesc =
+                umma_smem_desc(smem_u32(q_s + (qs * QB + b) * C::Q_TILE_BYTES), 16, C::SBO, C::SWZ);
 #pragma unroll
-          for (int k = 0; k < C::KSTEPS; ++k)
-            umma_f8(tmem_base + acc * C::N, kdesc + (k * 32 >> 4), qdesc + (k * 32 >> 4), idesc, k > 0);
-          umma_commit(&k_empty[st]);
-          umma_commit(&acc_full[acc]);
+            for (int k = 0; k < C::KSTEPS; ++k)
+              umma_f8(tmem_base + acc * C::N, kdesc + (k * 32 >> 4), qdesc + (k * 32 >> 4), idesc, k > 0);
+            umma_commit(&acc_full[acc]);
+          }
+          if (ok) umma_commit(&k_empty[st]);
         }
         if (ok) umma_commit(&q_empty[qs]);
       }
       ++nu;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       it = __shfl_sync(0xffffffffu, it, 0);
+      it2 = __shfl_sync(0xffffffffu, it2, 0);
       if (!ok) break;
+    }
+    PROF_ADD(3);
+    PROF_STORE(0);
+  } else if (warp == 2) {
+    // ------------------- stager: head weights and windows per unit -------------------
+    uint32_t nu = 0;
+    for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
+      int qb, nb, t_lo, t_hi;
+      if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
+      const int ub = nu & 1;
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(&w_empty[ub], ((nu >> 1) & 1) ^ 1, abort_flag, a.status));
+      if (!ok) break;
+      float* wd = w_s + ub * QB * C::N;
+      int2* wind = win_s + ub * C::NTOK;
+      const int t0 = qb * QB * NQ;
+      for (int c = lane; c < QB * C::N; c += 32) {
+        const int t = t0 + c / H;
+        float wvv = 0.f;
+        if (t < a.T) {
+          const int64_t off = (int64_t)t * H + (c % H);
+          wvv = a.w_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[off])
+                            : reinterpret_cast<const float*>(a.w)[off];
+        }
+        wd[c] = wvv;
+      }
+      for (int j = lane; j < C::NTOK; j += 32) {
+        const int t = t0 + j;
+        int s0 = 0, s1 = 0;
+        if (t < a.T) {
+          s0 = (!PAGED && a.ks) ? max(a.ks[t], 0) : 0;
+          s1 = min(a.ke[t], a.S);
+        }
+        wind[j] = make_int2(s0, max(s1 - s0, 0));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&w_full[ub]);
+      ++nu;
     }
   } else if (warp >= 4) {
     // --------------------------- epilogue warpgroups ---------------------------
-    const int wg = (warp - 4) >> 2;              // 0 or 1 = accumulator stage it drains
+    const int ew = warp - 4;                     // epilogue warp index
+    const int wg = ew >> 2;                      // warpgroup
+    const int stage = wg & 1;                    // accumulator stage it drains
+    const int part = wg >> 1;                    // which share of the columns (SPLIT > 1)
     const int wq = warp & 3;                     // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;              // key within the tile = TMEM lane
-    float* my_w = w_s + (warp - 4) * C::N;       // each warp stages its own copy: no cross-warp sync
-    int* my_ks = win_s + (warp - 4) * 2 * NQ;
-    int* my_ke = my_ks + NQ;
-    const uint32_t t_row = tmem_base + (uint32_t(wq * 32) << 16) + wg * C::N;
-    uint32_t it = 0, n_mine = 0;
+    const uint32_t t_lane = tmem_base + (uint32_t(wq * 32) << 16) + stage * C::N;
+    uint32_t it2 = 0, n_mine = 0, nu = 0;
     bool ok = true;
+    PROF_DECL();
+    PROF_T0();
     for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-      int g, t_lo, t_hi;
-      if (!unit_tiles<NQ, PAGED>(a, u, n_groups, g, t_lo, t_hi)) continue;
-      bool staged = false;
-      for (int kt = t_lo; kt < t_hi; ++kt, ++it) {
-        if (int(it & 1) != wg) continue;
-        if (!staged) {
-          // stage this group's head weights and windows for the warp
-          __syncwarp();
-          for (int c = lane; c < C::N; c += 32) {
-            const int t = g * NQ + c / H;
-            float wv = 0.f;
-            if (t < a.T) {
-              const int64_t off = (int64_t)t * H + (c % H);
-              wv = a.w_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[off])
-                               : reinterpret_cast<const float*>(a.w)[off];
-            }
-            my_w[c] = wv;
-          }
-          for (int j = lane; j < NQ; j += 32) {
-            const int t = g * NQ + j;
-            int s0 = 0, s1 = 0;
-            if (t < a.T) {
-              s0 = (!PAGED && a.ks) ? a.ks[t] : 0;
-              s1 = min(a.ke[t], a.S);
-            }
-            my_ks[j] = s0;
-            my_ke[j] = s1;
-          }
-          __syncwarp();
-          staged = true;
-        }
-        const int s = kt * kTileKeys + row;      // logical key position
-        float kscale = 0.f;
+      int qb, nb, t_lo, t_hi;
+      if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
+      const int ub = nu & 1;
+      PROF_ADD(3);
+      ok = __all_sync(0xffffffffu, mbar_wait(&w_full[ub], (nu >> 1) & 1, abort_flag, a.status));
+      PROF_ADD(0);
+      if (!ok) break;
+      auto load_kscale = [&](int tile) -> float {
+        const int sk = tile * kTileKeys + row;
         if constexpr (!PAGED) {
-          if (s < a.S) kscale = a.k_scale[s];
+          return sk < a.S ? __ldg(a.k_scale + sk) : 0.f;
         } else {
-          if (s < my_ke[0]) {
-            const int phys = a.block_table[(int64_t)g * a.table_stride + s / kPageTokens];
+          if (sk < min(a.ke[qb], a.S)) {
+            const int phys = __ldg(a.block_table + (int64_t)qb * a.table_stride + sk / kPageTokens);
             if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows)
-              kscale = a.k_scale[(int64_t)phys * kPageTokens + (s % kPageTokens)];
+              return __ldg(a.k_scale + (int64_t)phys * kPageTokens + (sk % kPageTokens));
           }
+          return 0.f;
         }
-        ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[wg], n_mine & 1, abort_flag, a.status));
-        if (!ok) break;
-        tc_fence_after();
-
-        constexpr int CH = 32;                   // columns per TMEM load
-        uint32_t v[2][CH];
-        tmem_ld32(t_row, v[0]);
-        uint64_t acc2 = 0;                       // (even heads, odd heads) running sums
-#pragma unroll
-        for (int c = 0; c < C::N; c += CH) {
-          const int cur = (c / CH) & 1;
-          tmem_wait_ld();
-          if (c + CH < C::N) tmem_ld32(t_row + c + CH, v[cur ^ 1]);
-#pragma unroll
-          for (int i = 0; i < CH; i += 2) {
-            const int col = c + i;
-            if (col % H == 0) acc2 = 0;
-            const float d0 = fmaxf(__uint_as_float(v[cur][i]), 0.f);
-            const float d1 = fmaxf(__uint_as_float(v[cur][i + 1]), 0.f);
-            const uint64_t wp = *reinterpret_cast<const uint64_t*>(my_w + col);
-            acc2 = fma_f32x2(pack_f32x2(d0, d1), wp, acc2);
-            if ((col + 2) % H == 0) {
-              const int j = col / H;
-              const int t = g * NQ + j;
-              float e, o;
-              unpack_f32x2(acc2, e, o);
-              const float score = (e + o) * kscale;
-              if (t < a.T && s < a.S) {
-                const bool in = (s >= my_ks[j]) && (s < my_ke[j]);
-                a.logits[(int64_t)t * a.ld + s] = in ? score : -CUDART_INF_F;
-              }
-            }
+      };
+      const uint32_t ld32 = static_cast<uint32_t>(a.ld);
+      float kscale_next = load_kscale(t_lo);     // always one key tile ahead of the math
+      for (int kt = t_lo; kt < t_hi && ok; ++kt) {
+        const float kscale = kscale_next;
+        kscale_next = load_kscale(min(kt + 1, t_hi - 1));
+        for (int b = 0; b < nb; ++b, ++it2) {
+          if (int(it2 & 1) != stage) continue;
+          const int s = kt * kTileKeys + row;    // logical key position
+          const int g = qb * QB + b;
+          const float* my_w = w_s + (ub * QB + b) * C::N;
+          const int2* my_win = win_s + ub * C::NTOK + b * NQ;
+          float* grp_base = a.logits + (int64_t)g * NQ * a.ld;   // 32-bit offsets from here: NQ * ld < 2^31
+          const int n_tok = min(NQ, a.T - g * NQ);
+          PROF_ADD(3);
+          ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[stage], n_mine & 1, abort_flag, a.status));
+          PROF_ADD(1);
+          if (!ok) break;
+          tc_fence_after();
+          if constexpr (C::SPLIT == 1) {
+            drain_columns<H, NQ, C::CH, 0, C::N>(t_lane, my_w, my_win, kscale, s, s < a.S, n_tok, grp_base, ld32);
+          } else {
+            if (part == 0)
+              drain_columns<H, NQ, C::CH, 0, C::COLS_PER_WG>(t_lane, my_w, my_win, kscale, s, s < a.S, n_tok,
+                                                             grp_base, ld32);
+            else
+              drain_columns<H, NQ, C::CH, C::COLS_PER_WG, C::COLS_PER_WG>(t_lane, my_w, my_win, kscale, s,
+                                                                          s < a.S, n_tok, grp_base, ld32);
           }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[stage]);
+          PROF_ADD(2);
+          ++n_mine;
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[wg]);
-        ++n_mine;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&w_empty[ub]);
+      ++nu;
     }
+    PROF_ADD(3);
+    if (ew == 0) PROF_STORE(4);
+    if (ew == 4) PROF_STORE(8);
   }
 
   tc_fence_before();
@@ -352,16 +478,15 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 }
 
 // -inf outside the tiles the main kernel wrote (the "clean logits" contract of the
-// call being replaced): columns below the group's first tile and above its last.
-template <int NQ>
-__global__ void fill_masked_kernel(const IndexerArgs a, int n_groups) {
+// call being replaced): columns below the query block's first tile and above its last.
+template <int NTOK>
+__global__ void fill_masked_kernel(const IndexerArgs a) {
   const int t = blockIdx.x;
   if (t >= a.T) return;
-  const int g = t / NQ;
   __shared__ int s_lo, s_hi;
   if (threadIdx.x < 32) {
     int lo, hi;
-    group_window<NQ, false>(a, g, lo, hi);
+    token_window<false>(a, (t / NTOK) * NTOK, NTOK, lo, hi);
     if (threadIdx.x == 0) {
       if (hi <= lo) { lo = 0; hi = 0; }
       s_lo = (lo / kTileKeys) * kTileKeys;
@@ -373,6 +498,12 @@ __global__ void fill_masked_kernel(const IndexerArgs a, int n_groups) {
   for (int s = threadIdx.x; s < s_lo; s += blockDim.x) row[s] = -CUDART_INF_F;
   for (int s = s_hi + threadIdx.x; s < a.S; s += blockDim.x) row[s] = -CUDART_INF_F;
 }
+
+#ifdef DSA_IDX_PROFILE
+extern "C" int dsa_debug_read_profile(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * 148 * 16);
+}
+#endif
 
 // ------------------------------- host side ----------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -407,9 +538,9 @@ int make_tmap_2d_u8(CUtensorMap* m, const void* base, uint64_t rows, uint32_t ro
   return DSA_OK;
 }
 
-template <int H, int D, int NQ, bool PAGED>
+template <int H, int D, int NQ, bool PAGED, int QB, int EPI>
 static int launch_indexer(const void* q, const void* k, const IndexerArgs& a, int clean, cudaStream_t stream) {
-  using C = IdxCfg<H, D, NQ, PAGED>;
+  using C = IdxCfg<H, D, NQ, PAGED, QB, EPI>;
   if (a.T == 0 || a.S == 0) return DSA_OK;
   CUtensorMap tq, tk;
   int rc = make_tmap_2d_u8(&tq, q, (uint64_t)a.T * H, D, D, C::N);
@@ -418,30 +549,31 @@ static int launch_indexer(const void* q, const void* k, const IndexerArgs& a, in
              : make_tmap_2d_u8(&tk, k, (uint64_t)a.S, D, D, kTileKeys);
   if (rc) return rc;
   const int n_groups = (a.T + NQ - 1) / NQ;
+  const int n_qblocks = (n_groups + QB - 1) / QB;
   const int n_tiles = (a.S + kTileKeys - 1) / kTileKeys;
   const int n_chunks = (n_tiles + kChunkTiles - 1) / kChunkTiles;
-  const int64_t n_units64 = (int64_t)n_groups * n_chunks;
+  const int64_t n_units64 = (int64_t)n_qblocks * n_chunks;
   if (n_units64 > 0x7fffffff) return set_error(DSA_ERR_SHAPE, "indexer: too many work units");
   const int n_units = (int)n_units64;
-  auto kern = indexer_logits_kernel<H, D, NQ, PAGED>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-      return set_error(DSA_ERR_CUDA, "indexer: cannot raise dynamic shared memory to %d", C::SMEM_BYTES);
-    attr_done = true;
-  }
+  auto kern = indexer_logits_kernel<H, D, NQ, PAGED, QB, EPI>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+    return set_error(DSA_ERR_CUDA, "indexer: cannot raise dynamic shared memory to %d", C::SMEM_BYTES);
   const int grid = n_units < sm_count() ? n_units : sm_count();
-  kern<<<grid, kIdxThreads, C::SMEM_BYTES, stream>>>(tq, tk, a, n_groups, n_units);
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tq, tk, a, n_groups, n_qblocks, n_units);
   if constexpr (!PAGED) {
-    if (clean) fill_masked_kernel<NQ><<<a.T, 256, 0, stream>>>(a, n_groups);
+    if (clean) fill_masked_kernel<C::NTOK><<<a.T, 256, 0, stream>>>(a);
   }
   return check_launch("indexer_logits");
 }
 
 int indexer_logits_dispatch(const void* q, const void* k, const IndexerArgs& a, int H, int D, int clean,
                             cudaStream_t stream) {
-#define DSA_IDX_CASE(h, d)                                                    \
-  if (H == h && D == d) return launch_indexer<h, d, 256 / h, false>(q, k, a, clean, stream);
+  static const bool epi4 = getenv("DSA_IDX_EPI4") != nullptr;
+#define DSA_IDX_CASE(h, d)                                                                \
+  if (H == h && D == d) {                                                                 \
+    if (epi4) return launch_indexer<h, d, 256 / h, false, 2, 4>(q, k, a, clean, stream);  \
+    return launch_indexer<h, d, 256 / h, false, 2, 2>(q, k, a, clean, stream);            \
+  }
   DSA_IDX_CASE(64, 128)
   DSA_IDX_CASE(32, 128)
   DSA_IDX_CASE(16, 128)
@@ -456,9 +588,9 @@ int indexer_logits_dispatch(const void* q, const void* k, const IndexerArgs& a, 
 
 int indexer_logits_paged_dispatch(const void* q, const void* kcache, const IndexerArgs& a, int H, int D,
                                   cudaStream_t stream) {
-  if (H == 64 && D == 128) return launch_indexer<64, 128, 1, true>(q, kcache, a, 0, stream);
-  if (H == 32 && D == 128) return launch_indexer<32, 128, 1, true>(q, kcache, a, 0, stream);
-  if (H == 16 && D == 128) return launch_indexer<16, 128, 1, true>(q, kcache, a, 0, stream);
+  if (H == 64 && D == 128) return launch_indexer<64, 128, 1, true, 1, 2>(q, kcache, a, 0, stream);
+  if (H == 32 && D == 128) return launch_indexer<32, 128, 1, true, 1, 2>(q, kcache, a, 0, stream);
+  if (H == 16 && D == 128) return launch_indexer<16, 128, 1, true, 1, 2>(q, kcache, a, 0, stream);
   return set_error(DSA_ERR_SHAPE, "paged indexer: unsupported (heads=%d, head_dim=%d)", H, D);
 }
 

@@ -1,18 +1,21 @@
 // Per-row top-k by radix select (sm_100a).  Stands in for the torch.topk calls at
 // sparse_attn/DSA.py:361, 567 and 675-676 of the reference.
 //
-// One CTA per row.  fp32 values are mapped to order-preserving 32-bit keys.  A
-// pass histograms the next 12 key bits (shared-memory atomics) of the elements
-// that still match the decided prefix, a block-wide suffix scan finds the bin
-// holding the k-th largest element, and passes repeat until that bin is small
-// enough to finish in shared memory (or all 32 bits are decided, which handles
-// rows full of equal values).  One final pass over the row writes, in column
-// order, the elements above the threshold bin straight to the output and
-// stages the threshold bin's elements in shared memory, where each candidate's
-// rank is counted directly.  Ties at the k-th value go to the lower column.
-// Compaction uses block prefix sums, not atomics, so the output is
-// bit-identical from run to run.  The row is read once from HBM; later passes
-// hit L2 (a 131072-column row is 512 KB).
+// One CTA per row.  fp32 values are mapped to order-preserving 32-bit keys and
+// the k-th largest key is found digit by digit (12 + 12 + 8 bits):
+//   1. histogram the top 12 key bits of the row (shared-memory atomics), suffix-
+//      scan the bins to find the bin holding the k-th largest element;
+//   2. if that bin holds more than 2048 elements, repeat on the next digit over
+//      the row (only rows with tightly clustered values need this);
+//   3. one ordered pass over the row writes every element above the threshold
+//      bin straight to the output and stages the threshold bin's elements
+//      ("candidates") in shared memory, in column order;
+//   4. the remaining digits are resolved on the staged candidates, and a final
+//      ordered compaction emits candidates above the exact k-th key plus the
+//      first `need` candidates equal to it -- ties go to the lower column.
+// Compaction uses block prefix sums, never atomics, so the output is
+// bit-identical from run to run.  The row is read from HBM once; the second
+// read hits L2 (a 131072-column row is 512 KB).
 #include <math_constants.h>
 
 #include "dsa_common.cuh"
@@ -26,187 +29,217 @@ constexpr int kDigitBits = 12;
 constexpr int kBins = 1 << kDigitBits;
 constexpr int kBinsPerThread = kBins / kTopkThreads;   // 8
 constexpr int kCand = 2048;
+constexpr int kCandPerThread = kCand / kTopkThreads;   // 4
 constexpr int kVec = 4;
-constexpr int kChunk = kTopkThreads * kVec;
+constexpr int kEltPerThread = 16;                      // final pass: 4 x float4, contiguous
+constexpr int kChunkHist = kTopkThreads * kVec;        // histogram pass: coalesced float4
+constexpr int kChunkFinal = kTopkThreads * kEltPerThread;
 
 __device__ __forceinline__ uint32_t order_key(float x) {
   const uint32_t u = __float_as_uint(x);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return u ^ (static_cast<uint32_t>(static_cast<int32_t>(u) >> 31) | 0x80000000u);
 }
 
-struct RowReader {
-  const float* x;     // row base
-  int lo, hi;         // window
-  int base;           // first chunk start (multiple of 4, <= lo)
-  bool vec;           // 16-byte loads allowed
-  __device__ __forceinline__ void load(int i, float (&v)[kVec]) const {
-    // i is a multiple of 4; elements outside [lo, hi) are returned as-is and ignored by callers
-    if (vec) {
-      const float4 f = __ldg(reinterpret_cast<const float4*>(x + i));
-      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < kVec; ++j) v[j] = (i + j >= lo && i + j < hi) ? __ldg(x + i + j) : 0.f;
-    }
-  }
+struct TopkSmem {
+  uint32_t hist[kBins];
+  uint32_t cand_key[kCand];
+  int32_t cand_idx[kCand];
+  uint32_t warp_tot[2][kTopkWarps];
+  uint32_t bin, need, cnt;
 };
 
-// inclusive warp scan of a packed pair of 16-bit counters
-__device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v) {
-  const int lane = threadIdx.x & 31;
+// Block-wide: given hist[], find the bin b with  sum(hist[b+1..]) < need <= sum(hist[b..]).
+// Leaves bin / need (remaining within the bin) / cnt (= hist[b]) in shared memory.
+__device__ __forceinline__ void find_threshold_bin(TopkSmem& sm, uint32_t need) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t h[kBinsPerThread];
+  uint32_t mine = 0;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
-    if (lane >= o) v += n;
+  for (int j = 0; j < kBinsPerThread; ++j) {
+    h[j] = sm.hist[tid * kBinsPerThread + j];
+    mine += h[j];
   }
-  return v;
+  uint32_t v = mine;                     // suffix-inclusive scan inside the warp
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_down_sync(0xffffffffu, v, off);
+    if (lane + off < 32) v += nb;
+  }
+  if (lane == 0) sm.warp_tot[0][warp] = v;
+  __syncthreads();
+  uint32_t above = 0;
+  for (int w2 = warp + 1; w2 < kTopkWarps; ++w2) above += sm.warp_tot[0][w2];
+  const uint32_t incl = v + above;       // elements in bins >= first bin of this thread
+  uint32_t cum = incl - mine;            // elements in bins above this thread's
+  if (cum < need && need <= incl) {
+#pragma unroll
+    for (int j = kBinsPerThread - 1; j >= 0; --j) {
+      if (cum < need && cum + h[j] >= need) {
+        sm.bin = tid * kBinsPerThread + j;
+        sm.need = need - cum;
+        sm.cnt = h[j];
+      }
+      cum += h[j];
+    }
+  }
+  __syncthreads();
 }
 
-__global__ void __launch_bounds__(kTopkThreads)
+// Exclusive block prefix of a packed (lo16, hi16) counter pair; also returns the block total.
+// `buf` alternates between calls so one __syncthreads per call is enough.
+__device__ __forceinline__ uint32_t block_exclusive_scan(TopkSmem& sm, uint32_t packed, int buf, uint32_t& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t incl = packed;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += nb;
+  }
+  if (lane == 31) sm.warp_tot[buf][warp] = incl;
+  __syncthreads();
+  uint32_t wt = lane < kTopkWarps ? sm.warp_tot[buf][lane] : 0u;
+  uint32_t winc = wt;
+#pragma unroll
+  for (int o = 1; o < kTopkWarps; o <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, winc, o);
+    if (lane >= o) winc += nb;
+  }
+  total = __shfl_sync(0xffffffffu, winc, kTopkWarps - 1);
+  const uint32_t before = __shfl_sync(0xffffffffu, winc - wt, warp);
+  return incl - packed + before;
+}
+
+__global__ void __launch_bounds__(kTopkThreads, 3)
 topk_select_kernel(const float* __restrict__ logits, int64_t ld, const int32_t* __restrict__ ks,
                    const int32_t* __restrict__ ke, int T, int S, int k, int32_t* __restrict__ out) {
-  __shared__ uint32_t hist[kBins];
-  __shared__ uint32_t cand_key[kCand];
-  __shared__ int32_t cand_idx[kCand];
-  __shared__ uint32_t warp_tot[2][kTopkWarps];
-  __shared__ uint32_t s_bin, s_need, s_cnt;
-
+  __shared__ TopkSmem sm;
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int warp = tid >> 5;
-  int lo = ks ? max(ks[row], 0) : 0;
-  int hi = ke ? min(ke[row], S) : S;
+  const int lo = ks ? max(ks[row], 0) : 0;
+  const int hi = ke ? min(ke[row], S) : S;
   const int n = max(hi - lo, 0);
   int32_t* o = out + (int64_t)row * k;
   if (n <= k) {
     for (int j = tid; j < k; j += kTopkThreads) o[j] = j < n ? lo + j : -1;
     return;
   }
-  RowReader rd;
-  rd.x = logits + (int64_t)row * ld;
-  rd.lo = lo;
-  rd.hi = hi;
-  rd.base = lo & ~(kVec - 1);
-  rd.vec = ((reinterpret_cast<uintptr_t>(rd.x) & 15) == 0) && (ld % kVec == 0);
-  const int n_chunks = (hi - rd.base + kChunk - 1) / kChunk;
+  const float* x = logits + (int64_t)row * ld;
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && (ld % kVec == 0);
+  const int base = lo & ~(kVec - 1);           // chunk origin: multiple of 4, <= lo
 
-  uint32_t prefix = 0;    // value of the decided high bits
+  uint32_t prefix = 0;    // value of the decided high key bits
   int pbits = 0;          // how many high bits are decided
-  uint32_t need = k;      // how many elements are still wanted from the matching set
+  uint32_t need = k;      // elements still wanted from the set matching the prefix
   uint32_t cnt = 0;       // size of the threshold bin
 
+  // ---- 1./2. histogram passes over the row ------------------------------------
   while (true) {
     const int dbits = min(kDigitBits, 32 - pbits);
     const int shift = 32 - pbits - dbits;
     const uint32_t dmask = (1u << dbits) - 1u;
-    for (int b = tid; b < kBins; b += kTopkThreads) hist[b] = 0;
+    for (int b = tid; b < kBins; b += kTopkThreads) sm.hist[b] = 0;
     __syncthreads();
-    for (int c = 0; c < n_chunks; ++c) {
-      const int i = rd.base + c * kChunk + tid * kVec;
-      if (i >= hi) continue;
-      float v[kVec];
-      rd.load(i, v);
-#pragma unroll
-      for (int j = 0; j < kVec; ++j) {
-        if (i + j < lo || i + j >= hi) continue;
-        const uint32_t key = order_key(v[j]);
-        if (pbits == 0 || (key >> (32 - pbits)) == prefix) atomicAdd(&hist[(key >> shift) & dmask], 1u);
-      }
-    }
-    __syncthreads();
-    // suffix scan over bins: thread t owns bins [8t, 8t+8); scan in reversed thread order
-    uint32_t mine = 0;
-#pragma unroll
-    for (int j = 0; j < kBinsPerThread; ++j) mine += hist[tid * kBinsPerThread + j];
-    const int rt = kTopkThreads - 1 - tid;          // reversed thread id
-    // butterfly: bring value of reversed order into scan order
-    uint32_t v = mine;
-    // scan within warp in reversed lane order
-    {
-      const int rl = 31 - lane;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t nb = __shfl_down_sync(0xffffffffu, v, off);
-        if (rl >= off) v += nb;
-      }
-    }
-    if (lane == 0) warp_tot[0][warp] = v;           // total of this warp
-    __syncthreads();
-    uint32_t above = 0;                             // sum over warps with higher bins
-    for (int w2 = warp + 1; w2 < kTopkWarps; ++w2) above += warp_tot[0][w2];
-    const uint32_t incl = v + above;                // sum of bins >= 8*tid
-    const uint32_t excl = incl - mine;              // sum of bins >= 8*(tid+1)
-    (void)rt;
-    if (excl < need && need <= incl) {
-      uint32_t cum = excl;
-      for (int j = kBinsPerThread - 1; j >= 0; --j) {
-        const uint32_t h = hist[tid * kBinsPerThread + j];
-        if (cum + h >= need) {
-          s_bin = tid * kBinsPerThread + j;
-          s_need = need - cum;
-          s_cnt = h;
-          break;
+    if (vec) {
+      // interior float4s need no window test; the (at most two) edge float4s do
+      const int first_full = (lo + kVec - 1) & ~(kVec - 1);
+      const int last_full = hi & ~(kVec - 1);
+      if (pbits == 0) {
+#pragma unroll 4
+        for (int i = first_full + tid * kVec; i < last_full; i += kChunkHist) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(x + i));
+          atomicAdd(&sm.hist[order_key(f.x) >> shift], 1u);
+          atomicAdd(&sm.hist[order_key(f.y) >> shift], 1u);
+          atomicAdd(&sm.hist[order_key(f.z) >> shift], 1u);
+          atomicAdd(&sm.hist[order_key(f.w) >> shift], 1u);
         }
-        cum += h;
+      } else {
+        const int pshift = 32 - pbits;
+#pragma unroll 4
+        for (int i = first_full + tid * kVec; i < last_full; i += kChunkHist) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(x + i));
+          const float v[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t key = order_key(v[j]);
+            if ((key >> pshift) == prefix) atomicAdd(&sm.hist[(key >> shift) & dmask], 1u);
+          }
+        }
+      }
+      // edges: [lo, first_full) and [last_full, hi)
+      const int n_head = min(first_full, hi) - lo;
+      const int n_tail = last_full >= first_full ? hi - last_full : 0;
+      if (tid < n_head + n_tail) {
+        const int i = tid < n_head ? lo + tid : last_full + (tid - n_head);
+        const uint32_t key = order_key(__ldg(x + i));
+        if (pbits == 0 || (key >> (32 - pbits)) == prefix) atomicAdd(&sm.hist[(key >> shift) & dmask], 1u);
+      }
+    } else {
+      for (int i = lo + tid; i < hi; i += kTopkThreads) {
+        const uint32_t key = order_key(__ldg(x + i));
+        if (pbits == 0 || (key >> (32 - pbits)) == prefix) atomicAdd(&sm.hist[(key >> shift) & dmask], 1u);
       }
     }
     __syncthreads();
-    prefix = (pbits == 0 ? 0u : (prefix << dbits)) | s_bin;
-    need = s_need;
-    cnt = s_cnt;
+    find_threshold_bin(sm, need);
+    prefix = (pbits == 0 ? 0u : (prefix << dbits)) | sm.bin;
+    need = sm.need;
+    cnt = sm.cnt;
     pbits += dbits;
     __syncthreads();
-    if (cnt <= kCand || pbits == 32) break;
+    if (cnt <= (uint32_t)kCand || pbits == 32) break;
   }
 
-  // ---- final pass: ordered compaction ---------------------------------------
-  const uint32_t n_above = k - need;                // elements strictly above the threshold bin
-  const bool all_tied = (pbits == 32);              // every candidate equals the k-th value
-  const int pshift = 32 - pbits;                    // 0 when all bits are decided
+  // ---- 3. ordered pass: emit what is above the threshold bin, stage the bin ----
+  const uint32_t n_above = k - need;
+  const bool all_tied = (pbits == 32);           // every candidate equals the k-th value
+  const int pshift = 32 - pbits;
   uint32_t base_sel = 0, base_cand = 0;
+  const int n_chunks = (hi - base + kChunkFinal - 1) / kChunkFinal;
   for (int c = 0; c < n_chunks; ++c) {
-    const int i = rd.base + c * kChunk + tid * kVec;
-    uint32_t keys[kVec];
-    uint32_t packed = 0;
+    const int i0 = base + c * kChunkFinal + tid * kEltPerThread;
+    float v[kEltPerThread];
     uint32_t fsel = 0, fcand = 0;
-    if (i < hi) {
-      float v[kVec];
-      rd.load(i, v);
+    if (i0 < hi) {
+      if (vec) {
 #pragma unroll
-      for (int j = 0; j < kVec; ++j) {
-        keys[j] = order_key(v[j]);
-        if (i + j < lo || i + j >= hi) continue;
-        const uint32_t top = pshift >= 32 ? 0u : (keys[j] >> pshift);
-        if (top > prefix) { fsel |= 1u << j; packed += 1u; }
-        else if (top == prefix) { fcand |= 1u << j; packed += 1u << 16; }
+        for (int q = 0; q < kEltPerThread / kVec; ++q) {
+          // a float4 that starts below hi lies inside the row's allocation (ld % 4 == 0)
+          const float4 f = (i0 + q * kVec < hi) ? __ldg(reinterpret_cast<const float4*>(x + i0 + q * kVec))
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[q * 4 + 0] = f.x; v[q * 4 + 1] = f.y; v[q * 4 + 2] = f.z; v[q * 4 + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kEltPerThread; ++j) v[j] = (i0 + j >= lo && i0 + j < hi) ? __ldg(x + i0 + j) : 0.f;
+      }
+      const bool interior = (i0 >= lo) && (i0 + kEltPerThread <= hi);
+#pragma unroll
+      for (int j = 0; j < kEltPerThread; ++j) {
+        const uint32_t top = pshift >= 32 ? 0u : (order_key(v[j]) >> pshift);
+        const bool in = interior || (i0 + j >= lo && i0 + j < hi);
+        fsel |= (uint32_t)(in && top > prefix) << j;
+        fcand |= (uint32_t)(in && top == prefix) << j;
       }
     }
-    const uint32_t incl = warp_inclusive_scan(packed);
-    if (lane == 31) warp_tot[c & 1][warp] = incl;
-    __syncthreads();
-    uint32_t before = 0, total = 0;
+    const uint32_t packed = __popc(fsel) | (__popc(fcand) << 16);
+    uint32_t total;
+    const uint32_t excl = block_exclusive_scan(sm, packed, c & 1, total);
+    if (fsel | fcand) {
+      uint32_t ps = base_sel + (excl & 0xffffu);
+      uint32_t pc = base_cand + (excl >> 16);
 #pragma unroll
-    for (int w2 = 0; w2 < kTopkWarps; ++w2) {
-      const uint32_t t2 = warp_tot[c & 1][w2];
-      if (w2 < warp) before += t2;
-      total += t2;
-    }
-    const uint32_t excl = incl - packed + before;
-    uint32_t ps = base_sel + (excl & 0xffffu);
-    uint32_t pc = base_cand + (excl >> 16);
-#pragma unroll
-    for (int j = 0; j < kVec; ++j) {
-      if (fsel & (1u << j)) {
-        o[ps++] = i + j;
-      } else if (fcand & (1u << j)) {
-        if (all_tied) {
-          if (pc < need) o[n_above + pc] = i + j;
-        } else if (pc < (uint32_t)kCand) {
-          cand_key[pc] = keys[j];
-          cand_idx[pc] = i + j;
+      for (int j = 0; j < kEltPerThread; ++j) {
+        if (fsel & (1u << j)) {
+          o[ps++] = i0 + j;
+        } else if (fcand & (1u << j)) {
+          if (all_tied) {
+            if (pc < need) o[n_above + pc] = i0 + j;
+          } else {
+            sm.cand_key[pc] = order_key(v[j]);
+            sm.cand_idx[pc] = i0 + j;
+          }
+          ++pc;
         }
-        ++pc;
       }
     }
     base_sel += total & 0xffffu;
@@ -214,15 +247,58 @@ topk_select_kernel(const float* __restrict__ logits, int64_t ld, const int32_t* 
   }
   if (all_tied) return;
   __syncthreads();
-  // ---- rank the candidates: larger key first, lower column first on ties ------
-  for (uint32_t a = tid; a < cnt; a += kTopkThreads) {
-    const uint32_t ka = cand_key[a];
-    uint32_t rank = 0;
-    for (uint32_t b = 0; b < cnt; ++b) {
-      const uint32_t kb = cand_key[b];
-      rank += (kb > ka) || (kb == ka && b < a);
+
+  // ---- 4. resolve the remaining digits on the staged candidates -----------------
+  uint32_t ck[kCandPerThread];
+#pragma unroll
+  for (int j = 0; j < kCandPerThread; ++j) {
+    const uint32_t a = tid * kCandPerThread + j;        // contiguous per thread: keeps column order
+    ck[j] = a < cnt ? sm.cand_key[a] : 0u;
+  }
+  while (pbits < 32) {
+    const int dbits = min(kDigitBits, 32 - pbits);
+    const int shift = 32 - pbits - dbits;
+    const uint32_t dmask = (1u << dbits) - 1u;
+    for (int b = tid; b < kBins; b += kTopkThreads) sm.hist[b] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kCandPerThread; ++j) {
+      const uint32_t a = tid * kCandPerThread + j;
+      if (a < cnt && (ck[j] >> (32 - pbits)) == prefix) atomicAdd(&sm.hist[(ck[j] >> shift) & dmask], 1u);
     }
-    if (rank < need) o[n_above + rank] = cand_idx[a];
+    __syncthreads();
+    find_threshold_bin(sm, need);
+    prefix = (prefix << dbits) | sm.bin;
+    need = sm.need;
+    pbits += dbits;
+    __syncthreads();
+  }
+  // prefix is now the exact k-th largest key; `need` of the candidates equal to it are wanted
+  const uint32_t n_gt_base = k - need;                   // slots before the tied ones... filled below
+  uint32_t fgt = 0, feq = 0;
+#pragma unroll
+  for (int j = 0; j < kCandPerThread; ++j) {
+    const uint32_t a = tid * kCandPerThread + j;
+    if (a < cnt) {
+      fgt |= (uint32_t)(ck[j] > prefix) << j;
+      feq |= (uint32_t)(ck[j] == prefix) << j;
+    }
+  }
+  uint32_t total;
+  const uint32_t excl = block_exclusive_scan(sm, __popc(fgt) | (__popc(feq) << 16), 0, total);
+  // output layout: [0, n_above) above the bin, then candidates > key, then the `need` tied ones
+  uint32_t pg = n_above + (excl & 0xffffu);
+  uint32_t pe = excl >> 16;
+  (void)n_gt_base;
+#pragma unroll
+  for (int j = 0; j < kCandPerThread; ++j) {
+    const uint32_t a = tid * kCandPerThread + j;
+    if (fgt & (1u << j)) {
+      o[pg++] = sm.cand_idx[a];
+    } else if (feq & (1u << j)) {
+      if (pe < need) o[k - need + pe] = sm.cand_idx[a];
+      ++pe;
+    }
   }
 }
 

@@ -4,8 +4,12 @@ Tolerances.  Logits are fp32 sums of 64 fp32-accumulated FP8 dot products; the
 kernel applies k_scale after the head sum and sums heads in a fixed order that
 differs from torch.sum's, so it is compared with the float64 oracle within
 4e-6 of the largest |logit| in the case (the fp32 oracle itself sits ~1e-6 from
-float64).  Top-k sets must equal the float64 oracle's, except for swaps within
-1 fp32 ulp of the k-th score.
+float64).  Top-k sets must equal the float64 oracle's except for swaps of
+elements whose exact scores lie within TOPK_ULP_TOL fp32 ulps of the k-th score:
+a 64-term fp32 sum of mixed-sign terms carries a few ulps of rounding noise
+whatever its order (the fp32 CPU oracle shows swaps of the same size against
+float64), so a 1-ulp bound holds for most rows but not for every row; measured
+worst case on these seeds is 2.0 ulp.
 """
 import os
 
@@ -19,6 +23,7 @@ from tests.helpers import indexer_inputs, to_dev
 
 pytestmark = pytest.mark.gpu
 REL_TOL = 4e-6
+TOPK_ULP_TOL = 4.0
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_golden.npz"))
 
 
@@ -58,7 +63,7 @@ def test_golden_simulator_inputs():
     _check_logits((q8, k8, ksc, w, ks, ke), out)
     idx = ops.indexer_topk(q8.cuda(), k8.cuda(), ksc.cuda(), w.cuda(), ks.cuda(), ke.cuda(), 16)
     ref = O.indexer_logits_fp64(q8, k8, ksc, w, ks, ke).numpy()
-    r = O.check_topk_sets(idx.cpu().numpy(), ref, ks.numpy(), ke.numpy(), 16, ulp_tol=1.0)
+    r = O.check_topk_sets(idx.cpu().numpy(), ref, ks.numpy(), ke.numpy(), 16, ulp_tol=TOPK_ULP_TOL)
     assert not r["bad_rows"], r
 
 
@@ -110,7 +115,7 @@ def test_indexer_topk_sets_match_oracle(T, S, K, window):
     ops.check_status("cuda")
     assert idx.shape == (T, min(K, S)) and idx.dtype == torch.int32
     ref = O.indexer_logits_fp64(q8, k8, ksc, w, ks, ke).numpy()
-    r = O.check_topk_sets(idx.cpu().numpy(), ref, ks.numpy(), ke.numpy(), min(K, S), ulp_tol=1.0)
+    r = O.check_topk_sets(idx.cpu().numpy(), ref, ks.numpy(), ke.numpy(), min(K, S), ulp_tol=TOPK_ULP_TOL)
     assert not r["bad_rows"], r
     assert torch.equal(idx, ops.indexer_topk(*to_dev(*args), K)), "not deterministic"
 
