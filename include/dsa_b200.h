@@ -95,6 +95,26 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_fp8, const float* k_scale,
                      const int32_t* ks, const int32_t* ke, int T, int S, int H, int D, int k, int32_t* out_idx,
                      void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* dsa_indexer_topk without a caller-supplied workspace.  No counterpart in the
+ * reference: it exists for hosts that cannot allocate device memory at the call
+ * site (a runtime that owns the whole device heap and forbids allocation inside
+ * its operator callbacks, a serving loop whose pool is frozen once it starts).
+ * Same inputs, outputs and results as dsa_indexer_topk; the fp32 logits scratch
+ * is a 64 MiB array built into the library, which every GPU that loads the
+ * library keeps until the process exits.  Limits and rules:
+ *   - min(T, 256) * round_up(S, 4) * 4 bytes must fit in 64 MiB (S <= 65536 when
+ *     T >= 256); larger problems are refused with DSA_ERR_WORKSPACE.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call outside any stream capture.
+ *   - All calls on one device share the array, which keeps whatever the last
+ *     call left there (every call overwrites what it reads).  Two calls whose
+ *     kernels overlap on the GPU (different streams) race: serialise them.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+size_t dsa_indexer_topk_static_max_bytes(void);
+int dsa_indexer_topk_static(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
+                            const int32_t* ks, const int32_t* ke, int T, int S, int H, int D, int k,
+                            int32_t* out_idx, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -180,3 +180,28 @@ def indexer_topk(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, workspace: Opti
                                _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out), _ptr(workspace), workspace.numel(),
                                _ptr(status_word(q_fp8.device)), _stream()))
     return out
+
+
+def indexer_topk_static(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``indexer_topk`` for callers that may not allocate: the logits scratch is the
+    64 MiB array built into the library (shared by every call on the device, so
+    calls that overlap on the GPU race).  ``out`` should be passed by such callers;
+    it is only created here when omitted.  Sizes beyond the array are refused."""
+    _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke)
+    T, H, D = q_fp8.shape
+    S = k_fp8.shape[0]
+    k = min(k, S)
+    for t in (q_fp8, k_fp8, weights, k_scale):
+        if not t.is_contiguous():
+            raise DsaError("indexer_topk_static takes contiguous tensors (it will not copy)")
+    if k_scale.dtype != torch.float32 or k_scale.numel() != S:
+        raise DsaError("k_scale must be fp32 with one entry per key")
+    ks = _as_i32(ks, T, "ks")
+    ke = _as_i32(ke, T, "ke")
+    if out is None:
+        out = torch.empty(T, k, dtype=torch.int32, device=q_fp8.device)
+    lib = _lib.load()
+    check(lib.dsa_indexer_topk_static(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
+                                      _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out),
+                                      _ptr(status_word(q_fp8.device)), _stream()))
+    return out
