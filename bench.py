@@ -282,10 +282,9 @@ def main():
     flops = 2.0 * HEADS * DIM * causal_keys                      # algorithmic flops of one launch
     achieved = flops / (k_ms * 1e-3) / 1e12
     peak_fp8 = 2.0 * peaks["bf16_tflops"]
-    traffic = None
-    tp = os.path.join(ROOT, "profiles", "roofline_traffic.json")
-    if os.path.exists(tp):
-        traffic = json.load(open(tp)).get("indexer_logits_dram_bytes_per_launch")
+    # dram__bytes_read + dram__bytes_write of the indexer kernel from one ncu capture of the 512-row reduced
+    # case (13.84 MB + 75.25 MB), scaled by the row count (traffic is proportional to query rows)
+    traffic = (13.84e6 + 75.25e6) * T_ROWS / 512
     topk_bytes = 4.0 * causal_keys + T_ROWS * TOPK * 4
 
     line = {
