@@ -95,6 +95,31 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_fp8, const float* k_scale,
                      const int32_t* ks, const int32_t* ke, int T, int S, int H, int D, int k, int32_t* out_idx,
                      void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* Token-sparse MLA attention, prefill (MQA over the shared latent KV):
+ *   out[t,h,:] = sum_j softmax_j(scale * q[t,h,:576] . kv[idx[t,j],:576]) * kv[idx[t,j],:512]
+ * over the slots with idx[t,j] >= 0; a row without any valid slot gives zeros.
+ * Takes the place of the block-sparse attention stand-in reached through
+ * register_sparse_fa().run (sparse_attn/DSA.py:208-249); the reference has no
+ * sparse-MLA kernel of its own.
+ *   q_bf16 [T, H, 576] bf16; kv_bf16 [S_kv, 576] bf16; idx [T, K] int32 positions
+ *   into kv (negative = empty; >= S_kv is skipped and sets status 2);
+ *   out_bf16 [T, H, 512] bf16.  All contiguous and 16-byte aligned.  Any H >= 1
+ *   (heads are processed in groups of 128). */
+int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_t* idx, void* out_bf16, int T, int H,
+                           int S_kv, int K, float scale, int32_t* status, void* stream);
+
+/* The same attention for decode over the paged FP8 latent cache (no counterpart
+ * in the reference, which has no cache: sparse_attn/DSA.py:475-477).  One query
+ * token per sequence; idx[b, j] is a logical position of sequence b, stored at
+ * cache row block_table[b, pos/64]*64 + pos%64.  A cache row is 656 bytes:
+ * 512 e4m3 latent values, 4 fp32 scales (one per 128 values), 64 bf16 rope
+ * values; latent = e4m3 * scale is rounded to bf16 before the tensor-core math.
+ *   q_bf16 [B, H, 576]; cache [num_pages*64, 656] bytes; block_table
+ *   [B, table_stride] int32; idx [B, K] int32; out_bf16 [B, H, 512]. */
+int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int32_t* block_table,
+                                int64_t table_stride, const int32_t* idx, void* out_bf16, int B, int H, int K,
+                                int num_pages, int max_ctx, float scale, int32_t* status, void* stream);
+
 /* dsa_indexer_topk without a caller-supplied workspace.  No counterpart in the
  * reference: it exists for hosts that cannot allocate device memory at the call
  * site (a runtime that owns the whole device heap and forbids allocation inside

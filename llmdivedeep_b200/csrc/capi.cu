@@ -49,6 +49,12 @@ int indexer_logits_paged(const void* q, const void* w, int w_dtype, const void* 
 int topk_select_launch(const float* logits, int64_t ld, const int32_t* ks, const int32_t* ke, int T, int S, int k,
                        int32_t* out, cudaStream_t stream);
 
+int sparse_mla_prefill_launch(const void* q, const void* kv, const int32_t* idx, void* out, int T, int H, int S_kv,
+                              int K, float scale, int32_t* status, cudaStream_t stream);
+int sparse_mla_decode_launch(const void* q, const void* cache, const int32_t* block_table, int64_t table_stride,
+                             const int32_t* idx, void* out, int B, int H, int K, int num_pages, int max_ctx,
+                             float scale, int32_t* status, cudaStream_t stream);
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace dsa
@@ -115,6 +121,40 @@ int dsa_topk_select(const float* logits, int64_t ld_logits, const int32_t* ks, c
   if (ld_logits < S) return set_error(DSA_ERR_SHAPE, "topk_select: ld_logits < S");
   if (k > 65535) return set_error(DSA_ERR_SHAPE, "topk_select: k (%d) exceeds 65535", k);
   return topk_select_launch(logits, ld_logits, ks, ke, T, S, k, out_idx, static_cast<cudaStream_t>(stream));
+}
+
+int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_t* idx, void* out_bf16, int T, int H,
+                           int S_kv, int K, float scale, int32_t* status, void* stream) {
+  g_err[0] = 0;
+  if (T < 0 || H < 0 || S_kv < 0 || K < 0) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: negative size");
+  if (T == 0 || H == 0) return DSA_OK;
+  if (!q_bf16 || !out_bf16 || (K > 0 && (!idx || !kv_bf16)))
+    return set_error(DSA_ERR_ARG, "sparse_mla_prefill: NULL pointer argument");
+  if (!aligned16(q_bf16) || !aligned16(kv_bf16) || !aligned16(out_bf16))
+    return set_error(DSA_ERR_ALIGN, "sparse_mla_prefill: q, kv and out must be 16-byte aligned");
+  if ((int64_t)T * H > 0x7fffffffLL || T > 0x7fffffff / 2) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: T*H too large");
+  if (H > 128 * 65535) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: too many heads");
+  return sparse_mla_prefill_launch(q_bf16, kv_bf16, idx, out_bf16, T, H, S_kv, K, scale, status,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int32_t* block_table,
+                                int64_t table_stride, const int32_t* idx, void* out_bf16, int B, int H, int K,
+                                int num_pages, int max_ctx, float scale, int32_t* status, void* stream) {
+  g_err[0] = 0;
+  if (B < 0 || H < 0 || K < 0 || num_pages < 0 || max_ctx < 0)
+    return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: negative size");
+  if (B == 0 || H == 0) return DSA_OK;
+  if (!q_bf16 || !out_bf16 || (K > 0 && (!idx || !cache || !block_table)))
+    return set_error(DSA_ERR_ARG, "sparse_mla_decode_paged: NULL pointer argument");
+  if (!aligned16(q_bf16) || !aligned16(cache) || !aligned16(out_bf16))
+    return set_error(DSA_ERR_ALIGN, "sparse_mla_decode_paged: q, cache and out must be 16-byte aligned");
+  if (table_stride * 64 < max_ctx)
+    return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: block table row shorter than max_ctx");
+  if ((int64_t)num_pages * 64 > 0x7fffffffLL || (int64_t)B * H > 0x7fffffffLL)
+    return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: problem too large");
+  return sparse_mla_decode_launch(q_bf16, cache, block_table, table_stride, idx, out_bf16, B, H, K, num_pages,
+                                  max_ctx, scale, status, static_cast<cudaStream_t>(stream));
 }
 
 static const int kMinChunkRows = 256;

@@ -519,23 +519,29 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// 2-D byte tensor [rows, row_bytes] with a [box_rows, row_bytes] box, swizzled by row_bytes.
-int make_tmap_2d_u8(CUtensorMap* m, const void* base, uint64_t rows, uint32_t row_bytes, uint64_t row_pitch,
-                    uint32_t box_rows) {
+// 2-D byte tensor [rows, inner_bytes] (row pitch in bytes) with a [box_rows, box_bytes] box whose
+// shared-memory image is swizzled by the box width (128 or 64 bytes).
+int make_tmap_2d_bytes(CUtensorMap* m, const void* base, uint64_t rows, uint64_t inner_bytes, uint64_t row_pitch,
+                       uint32_t box_bytes, uint32_t box_rows) {
   auto fn = encode_fn();
   if (!fn) return set_error(DSA_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
-  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t dims[2] = {inner_bytes, rows};
   cuuint64_t strides[1] = {row_pitch};
-  cuuint32_t box[2] = {row_bytes, box_rows};
+  cuuint32_t box[2] = {box_bytes, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                        : row_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
+  CUtensorMapSwizzle sw = box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                        : box_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
                                            : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(DSA_ERR_CUDA, "cuTensorMapEncodeTiled failed (code %d)", (int)r);
   return DSA_OK;
+}
+
+int make_tmap_2d_u8(CUtensorMap* m, const void* base, uint64_t rows, uint32_t row_bytes, uint64_t row_pitch,
+                    uint32_t box_rows) {
+  return make_tmap_2d_bytes(m, base, rows, row_bytes, row_pitch, row_bytes, box_rows);
 }
 
 template <int H, int D, int NQ, bool PAGED, int QB, int EPI>

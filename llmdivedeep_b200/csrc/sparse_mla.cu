@@ -1,0 +1,398 @@
+// Token-sparse MLA attention on sm_100a (MQA over the shared 576-dim latent KV, 512-dim V):
+//   o[t, h, :] = sum_j softmax_j(scale * q[t, h, :] . kv[idx[t, j], :]) * kv[idx[t, j], :512]
+// Takes the place of the block-sparse stand-in the reference reaches through
+// register_sparse_fa() (sparse_attn/DSA.py:208-249); the reference itself has no sparse-MLA
+// kernel, no latent cache and no decode path (sparse_attn/DSA.py:475-477).
+//
+// One CTA per (query token, half of the V dimension, group of up to 128 heads).
+//   * Q [128 heads x 576] arrives by TMA as nine 128-byte-swizzled K-major panels (A operand).
+//   * The selected KV rows are gathered 64 at a time into nine [64 keys x 64 dims] panels with
+//     the same swizzle: cp.async from the bf16 KV, or -- for the paged FP8 latent cache of
+//     decode -- 16-byte loads, e4m3 -> bf16 with the per-128 group scale, 16-byte stores.
+//     A panel is the K-major B operand of S = Q K^T and, read with an MN-major descriptor, the
+//     B operand of O += P V: the rows are gathered once and used twice.
+//   * tcgen05.mma kind::f16 (bf16 in, fp32 out): S [128 x 64] and O [128 x 256] live in tensor
+//     memory; P is written back to tensor memory as packed bf16 and is the A operand of P V.
+//   * Online softmax with one thread per head (= TMEM lane): the row maximum and sum are
+//     thread-local; O is rescaled in tensor memory only when the running maximum grows by more
+//     than 8 (in log2 units), which keeps every exponent <= 2^8.
+// The two CTAs of a token each recompute S (the 512 fp32 columns of a full O would fill tensor
+// memory on their own); they share nothing and need no cluster.
+//
+// Roles: warps 0-3 softmax / output (thread = head), warp 4 lane 0 MMA issuer (warp 4 owns the
+// TMEM allocation), warps 5-8 gather.  Every wait is bounded (dsa_common.cuh).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_fp8.h>
+#include <math_constants.h>
+
+#include "dsa_common.cuh"
+#include "dsa_host.h"
+
+namespace dsa {
+
+constexpr int kMlaDqk = 576;
+constexpr int kMlaDv = 512;
+constexpr int kMlaDvHalf = 256;
+constexpr int kMlaBlk = 64;                       // keys per block
+constexpr int kMlaPanels = kMlaDqk / 64;          // 9 panels of 64 dims (128 bytes)
+constexpr int kMlaQPanelBytes = 128 * 128;        // 128 heads x 128 B
+constexpr int kMlaKPanelBytes = kMlaBlk * 128;    // 64 keys x 128 B
+constexpr int kMlaQBytes = kMlaPanels * kMlaQPanelBytes;   // 147456
+constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;   // 73728
+constexpr int kMlaThreads = 288;
+constexpr int kMlaGatherThreads = 128;
+constexpr int kMlaSmemBytes = 1024 + kMlaQBytes + kMlaKBytes + 1024;
+constexpr int kLatentTokenBytes = 656;            // 512 e4m3 + 4 fp32 scales + 64 bf16 rope
+constexpr int kLatentPage = 64;
+// tensor-memory columns
+constexpr uint32_t kColO = 0, kColS = 256, kColP = 320, kMlaTmemCols = 512;
+
+struct MlaArgs {
+  const __nv_bfloat16* kv;        // prefill: [S_kv, 576] bf16
+  const uint8_t* cache;           // decode: [num_pages*64, 656] bytes
+  const int32_t* block_table;     // decode: [B, table_stride]
+  const int32_t* idx;             // [T, K] selected key positions (negative = empty)
+  __nv_bfloat16* out;             // [T, H, 512]
+  int64_t table_stride;
+  int T, H, K;
+  int S_kv;                       // prefill: rows of kv; decode: logical positions per sequence
+  int num_phys_rows;              // decode: rows of the cache
+  float scale_log2e;              // softmax scale * log2(e)
+  int* status;
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;            // 0 source bytes = zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// Gather one block of 64 selected rows into the nine swizzled panels.  Thread g of 128.
+template <bool FP8_PAGED>
+__device__ __forceinline__ void gather_block(const MlaArgs& a, int t, const int32_t* __restrict__ idx_blk, int n_in_blk,
+                                             uint8_t* kv_s, uint8_t* valid_s, int g) {
+  // row ids (prefill: kv row; decode: physical cache row), -1 when the slot is empty / out of range
+  __shared__ int rows_s[kMlaBlk];
+  if (g < kMlaBlk) {
+    int r = -1;
+    if (g < n_in_blk) {
+      const int pos = idx_blk[g];
+      if (pos >= 0) {
+        if (pos >= a.S_kv) {
+          if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+        } else if constexpr (!FP8_PAGED) {
+          r = pos;
+        } else {
+          const int phys = a.block_table[(int64_t)t * a.table_stride + pos / kLatentPage];
+          if (phys >= 0 && (int64_t)(phys + 1) * kLatentPage <= a.num_phys_rows) r = phys * kLatentPage + pos % kLatentPage;
+          else if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+        }
+      }
+    }
+    rows_s[g] = r;
+    valid_s[g] = r >= 0;
+  }
+  named_bar_sync(1, kMlaGatherThreads);
+  if constexpr (!FP8_PAGED) {
+    // 64 rows x 72 chunks of 16 bytes
+#pragma unroll 4
+    for (int q = g; q < kMlaBlk * 72; q += kMlaGatherThreads) {
+      const int r = q / 72, cc = q - r * 72;
+      const int p = cc >> 3, c = cc & 7;
+      const int row = rows_s[r];
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv) + (int64_t)max(row, 0) * (kMlaDqk * 2) + cc * 16;
+      cp_async16(kv_s + p * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4), src, row >= 0);
+    }
+    cp_async_wait_all();
+  } else {
+    // latent: 64 rows x 32 chunks of 16 e4m3 -> two 16-byte bf16 chunks each; rope: 64 rows x 8 chunks
+    for (int q = g; q < kMlaBlk * 32; q += kMlaGatherThreads) {
+      const int r = q >> 5, cc = q & 31;               // cc: 16-element chunk of the 512 latent dims
+      const int row = rows_s[r];
+      uint4 o0 = make_uint4(0, 0, 0, 0), o1 = o0;
+      if (row >= 0) {
+        const uint8_t* rec = a.cache + (int64_t)row * kLatentTokenBytes;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rec + cc * 16));
+        const float sc = __ldg(reinterpret_cast<const float*>(rec + kMlaDv) + (cc >> 3));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t outw[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const __nv_fp8x2_storage_t pr = static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * hh)) & 0xffffu);
+            const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            outw[i * 2 + hh] = pack_bf16x2(f.x * sc, f.y * sc);
+          }
+        }
+        o0 = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+        o1 = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+      }
+      const int d0 = cc * 16;                          // first latent dim of this chunk
+      const int p = d0 >> 6, c = (d0 & 63) >> 3;       // panel, 16-byte chunk inside the 128-byte row (even)
+      uint8_t* base = kv_s + p * kMlaKPanelBytes + r * 128;
+      *reinterpret_cast<uint4*>(base + ((c ^ (r & 7)) << 4)) = o0;
+      *reinterpret_cast<uint4*>(base + (((c + 1) ^ (r & 7)) << 4)) = o1;
+    }
+    for (int q = g; q < kMlaBlk * 8; q += kMlaGatherThreads) {
+      const int r = q >> 3, c = q & 7;
+      const int row = rows_s[r];
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row >= 0) v = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)row * kLatentTokenBytes + kMlaDv + 16) + c);
+      *reinterpret_cast<uint4*>(kv_s + 8 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+    }
+  }
+  fence_async_smem();          // make the panel writes visible to the tensor core's reads
+}
+
+template <bool FP8_PAGED>
+__global__ void __launch_bounds__(kMlaThreads, 1)
+sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;                               // 9 panels [128 heads x 128 B]
+  uint8_t* kv_s = q_s + kMlaQBytes;                  // 9 panels [64 keys x 128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kMlaKBytes);
+  uint64_t* q_full = bars + 0;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_free = bars + 2;
+  uint64_t* s_full = bars + 3;
+  uint64_t* p_full = bars + 4;
+  uint64_t* o_final = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_s = const_cast<int*>(abort_flag) + 1;
+  uint8_t* valid_s = reinterpret_cast<uint8_t*>(last_s + 1);   // 64 flags of the current block
+
+  const int t = blockIdx.x, vhalf = blockIdx.y, hg = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int32_t* idx_row = a.idx + (int64_t)t * a.K;
+  const int heads_here = min(128, a.H - hg * 128);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(kv_full, kMlaGatherThreads);
+    mbar_init(kv_free, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_final, 1);
+    *abort_flag = 0;
+    *last_s = -1;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+  }
+  __syncthreads();
+  {  // last non-empty slot of this row decides how many 64-key blocks there are
+    int last = -1;
+    for (int j = threadIdx.x; j < a.K; j += kMlaThreads)
+      if (idx_row[j] >= 0) last = j;
+    if (last >= 0) atomicMax(last_s, last);
+  }
+  __syncthreads();
+  const int nblk = (*last_s + kMlaBlk) / kMlaBlk;
+  if (nblk == 0) {   // nothing selected: the output row is zero
+    if (threadIdx.x < 128 && threadIdx.x < heads_here) {
+      uint4* o = reinterpret_cast<uint4*>(a.out + ((int64_t)t * a.H + hg * 128 + threadIdx.x) * kMlaDv + vhalf * kMlaDvHalf);
+      for (int c = 0; c < kMlaDvHalf * 2 / 16; ++c) o[c] = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, kMlaTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(1, 1, 0, 0, 128, kMlaBlk);
+      constexpr uint32_t idesc_pv = umma_idesc(1, 1, 0, 1, 128, kMlaDvHalf);
+      mbar_expect_tx(q_full, kMlaQBytes);
+      for (int p = 0; p < kMlaPanels; ++p)
+        tma_load_2d(q_s + p * kMlaQPanelBytes, &tmap_q, p * 128, t * a.H + hg * 128, q_full);
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
+      const uint64_t vdesc = umma_smem_desc(smem_u32(kv_s + vhalf * 4 * kMlaKPanelBytes), kMlaKPanelBytes, 1024, kSwz128);
+      for (int j = 0; j < nblk && ok; ++j) {
+        ok = mbar_wait(kv_full, j & 1, abort_flag, a.status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int p = 0; p < kMlaPanels; ++p) {
+          const uint64_t qd = umma_smem_desc(smem_u32(q_s + p * kMlaQPanelBytes), 16, 1024, kSwz128);
+          const uint64_t kd = umma_smem_desc(smem_u32(kv_s + p * kMlaKPanelBytes), 16, 1024, kSwz128);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss(tmem + kColS, qd + 2 * ks, kd + 2 * ks, idesc_qk, (p | ks) != 0);
+        }
+        umma_commit(s_full);
+        ok = mbar_wait(p_full, j & 1, abort_flag, a.status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)      // 16 keys per step: 16 rows x 128 B further into each panel
+          umma_f16_ts(tmem + kColO, tmem + kColP + 8 * ks, vdesc + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
+        umma_commit(kv_free);
+        if (j == nblk - 1) umma_commit(o_final);
+      }
+    }
+  } else if (warp >= 5) {
+    // --------------------------------- gather ---------------------------------
+    const int g = threadIdx.x - 160;
+    for (int j = 0; j < nblk; ++j) {
+      mbar_wait(kv_free, (j & 1) ^ 1, abort_flag, a.status);
+      gather_block<FP8_PAGED>(a, t, idx_row + j * kMlaBlk, min(kMlaBlk, a.K - j * kMlaBlk), kv_s, valid_s, g);
+      mbar_arrive(kv_full);
+      if (*abort_flag) break;       // uniform: checked after the gather threads' own barrier
+    }
+  } else {
+    // ------------------------- softmax and output (thread = head) -------------------------
+    const int row = threadIdx.x;                       // 0..127 = TMEM lane
+    const uint32_t t_row = tmem + (uint32_t(warp * 32) << 16);
+    float m = -CUDART_INF_F, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, a.status));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[2][32];
+      tmem_ld32(t_row + kColS, sv[0]);
+      tmem_ld32(t_row + kColS + 32, sv[1]);
+      tmem_wait_ld();
+      float s[64];
+      float bmax = -CUDART_INF_F;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float x = __uint_as_float(sv[i >> 5][i & 31]) * a.scale_log2e;
+        s[i] = valid_s[i] ? x : -CUDART_INF_F;
+        bmax = fmaxf(bmax, s[i]);
+      }
+      const float m_new = fmaxf(m, bmax);
+      const bool grow = m_new - m > 8.f;               // also true when m is still -inf and m_new is finite
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = grow ? fast_exp2(m - m_new) : 1.f;
+        if (grow) m = m_new;
+        l *= alpha;
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < kMlaDvHalf; c += 32) {
+            uint32_t ov[32];
+            tmem_ld32(t_row + kColO + c, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st32(t_row + kColO + c, ov);
+          }
+        }
+      }
+      const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+      uint32_t pk[32];
+      float psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) {
+        const float p0 = fast_exp2(s[i] - m_eff), p1 = fast_exp2(s[i + 1] - m_eff);
+        psum += p0 + p1;
+        pk[i >> 1] = pack_bf16x2(p0, p1);
+      }
+      l += psum;
+      tmem_st32(t_row + kColP, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = a.out + ((int64_t)t * a.H + hg * 128 + row) * kMlaDv + vhalf * kMlaDvHalf;
+#pragma unroll 1
+      for (int c = 0; c < kMlaDvHalf; c += 32) {
+        uint32_t ov[32];
+        tmem_ld32(t_row + kColO + c, ov);
+        tmem_wait_ld();
+        if (row < heads_here) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(ov[i + 0]) * inv, __uint_as_float(ov[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(ov[i + 4]) * inv, __uint_as_float(ov[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(ov[i + 6]) * inv, __uint_as_float(ov[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c + i) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kMlaTmemCols);
+  }
+}
+
+int make_tmap_2d_bytes(CUtensorMap* m, const void* base, uint64_t rows, uint64_t inner_bytes, uint64_t row_pitch,
+                       uint32_t box_bytes, uint32_t box_rows);
+
+template <bool FP8_PAGED>
+static int launch_mla(const void* q, const MlaArgs& a, cudaStream_t stream) {
+  if (a.T == 0 || a.H == 0) return DSA_OK;
+  CUtensorMap tq;
+  int rc = make_tmap_2d_bytes(&tq, q, (uint64_t)a.T * a.H, kMlaDqk * 2, kMlaDqk * 2, 128, 128);
+  if (rc) return rc;
+  auto kern = sparse_mla_kernel<FP8_PAGED>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes) != cudaSuccess)
+    return set_error(DSA_ERR_CUDA, "sparse_mla: cannot raise dynamic shared memory to %d", kMlaSmemBytes);
+  const dim3 grid(a.T, 2, (a.H + 127) / 128);
+  kern<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tq, a);
+  return check_launch("sparse_mla");
+}
+
+int sparse_mla_prefill_launch(const void* q, const void* kv, const int32_t* idx, void* out, int T, int H, int S_kv,
+                              int K, float scale, int32_t* status, cudaStream_t stream) {
+  MlaArgs a{};
+  a.kv = static_cast<const __nv_bfloat16*>(kv);
+  a.idx = idx;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.T = T; a.H = H; a.K = K; a.S_kv = S_kv;
+  a.scale_log2e = scale * 1.4426950408889634f;
+  a.status = status;
+  return launch_mla<false>(q, a, stream);
+}
+
+int sparse_mla_decode_launch(const void* q, const void* cache, const int32_t* block_table, int64_t table_stride,
+                             const int32_t* idx, void* out, int B, int H, int K, int num_pages, int max_ctx,
+                             float scale, int32_t* status, cudaStream_t stream) {
+  MlaArgs a{};
+  a.cache = static_cast<const uint8_t*>(cache);
+  a.block_table = block_table;
+  a.table_stride = table_stride;
+  a.idx = idx;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.T = B; a.H = H; a.K = K; a.S_kv = max_ctx;
+  a.num_phys_rows = num_pages * kLatentPage;
+  a.scale_log2e = scale * 1.4426950408889634f;
+  a.status = status;
+  return launch_mla<true>(q, a, stream);
+}
+
+}  // namespace dsa

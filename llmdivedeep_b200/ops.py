@@ -205,3 +205,43 @@ def indexer_topk_static(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, out: Opt
                                       _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out),
                                       _ptr(status_word(q_fp8.device)), _stream()))
     return out
+
+
+def sparse_mla_prefill(q, kv, idx, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sparse MLA over selected latent-KV rows.  q [T,H,576] bf16, kv [S,576] bf16,
+    idx [T,K] int32 (negative = empty slot).  Returns bf16 [T,H,512]."""
+    _need_cuda(q, kv, idx)
+    if q.dtype != torch.bfloat16 or kv.dtype != torch.bfloat16 or idx.dtype != torch.int32:
+        raise DsaError("sparse_mla_prefill takes bf16 q/kv and int32 idx")
+    if q.dim() != 3 or q.shape[2] != 576 or kv.dim() != 2 or kv.shape[1] != 576 or idx.dim() != 2 or idx.shape[0] != q.shape[0]:
+        raise DsaError(f"bad shapes q {tuple(q.shape)} kv {tuple(kv.shape)} idx {tuple(idx.shape)}")
+    q, kv, idx = q.contiguous(), kv.contiguous(), idx.contiguous()
+    T, H, _ = q.shape
+    if out is None:
+        out = torch.empty(T, H, 512, dtype=torch.bfloat16, device=q.device)
+    lib = _lib.load()
+    check(lib.dsa_sparse_mla_prefill(_ptr(q), _ptr(kv), _ptr(idx), _ptr(out), T, H, kv.shape[0], idx.shape[1],
+                                     float(scale), _ptr(status_word(q.device)), _stream()))
+    return out
+
+
+def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: Optional[int] = None,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode step over the paged FP8 latent cache.  q [B,H,576] bf16, cache uint8
+    [num_pages*64, 656], block_table [B,P] int32, idx [B,K] int32 logical positions."""
+    _need_cuda(q, cache, block_table, idx)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.uint8 or idx.dtype != torch.int32 or block_table.dtype != torch.int32:
+        raise DsaError("sparse_mla_decode_paged takes bf16 q, uint8 cache, int32 block_table/idx")
+    if cache.dim() != 2 or cache.shape[1] != 656 or cache.shape[0] % 64:
+        raise DsaError("cache must be uint8 [num_pages*64, 656]")
+    q, cache, block_table, idx = q.contiguous(), cache.contiguous(), block_table.contiguous(), idx.contiguous()
+    B, H, _ = q.shape
+    if max_ctx is None:
+        max_ctx = block_table.shape[1] * 64
+    if out is None:
+        out = torch.empty(B, H, 512, dtype=torch.bfloat16, device=q.device)
+    lib = _lib.load()
+    check(lib.dsa_sparse_mla_decode_paged(_ptr(q), _ptr(cache), _ptr(block_table), block_table.stride(0), _ptr(idx),
+                                          _ptr(out), B, H, idx.shape[1], cache.shape[0] // 64, max_ctx, float(scale),
+                                          _ptr(status_word(q.device)), _stream()))
+    return out
