@@ -1,0 +1,94 @@
+"""How the DSA path is split over the GPUs of one box (one process per GPU).
+
+Nothing in the reference is distributed; these rules come from the structure of the path:
+  * prefill indexer + top-k: query rows are independent -> each rank takes whole chunks of
+    query rows, dealt in serpentine order so that the causal cost (row t scans t+1 keys) balances;
+    the keys are replicated; no exchange.
+  * prefill sparse MLA: by rows (same chunks, no exchange before the output) or by heads
+    (H/world heads per rank; needs every rank to hold all top-k indices).
+  * decode: sequences are independent -> contiguous slices of the batch.
+  * the only collective is the all-gather of the attention output.
+The helpers are pure index arithmetic plus one torch.distributed call, so they run under
+gloo on CPU as well as nccl on GPUs.
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def row_chunks(n_rows: int, world: int, rank: int, chunk: int = 256) -> List[Tuple[int, int]]:
+    """[start, end) query-row ranges of `rank`: chunks of `chunk` rows dealt in serpentine order
+    (0..world-1, then world-1..0, ...), which evens out the linearly growing causal cost."""
+    if not (0 <= rank < world) or chunk <= 0:
+        raise ValueError("bad rank/world/chunk")
+    n_chunks = (n_rows + chunk - 1) // chunk
+    out = []
+    for rnd in range((n_chunks + world - 1) // world):
+        c = rnd * world + (rank if rnd % 2 == 0 else world - 1 - rank)
+        if c < n_chunks:
+            out.append((c * chunk, min(n_rows, (c + 1) * chunk)))
+    return out
+
+
+def rows_of(chunks: List[Tuple[int, int]], device=None) -> torch.Tensor:
+    """Row indices covered by a list of ranges, ascending."""
+    if not chunks:
+        return torch.empty(0, dtype=torch.long, device=device)
+    return torch.cat([torch.arange(a, b, device=device) for a, b in chunks])
+
+
+def causal_cost(chunks: List[Tuple[int, int]], first_pos: int = 0) -> int:
+    """Keys scanned by the causal indexer for these rows (row t scans first_pos + t + 1 keys)."""
+    return sum((b - a) * (2 * first_pos + a + b + 1) // 2 for a, b in chunks)
+
+
+def head_range(n_heads: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous slice of attention heads of `rank` (sizes differ by at most one)."""
+    base, extra = divmod(n_heads, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def batch_range(batch: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous slice of decode sequences of `rank`."""
+    return head_range(batch, world, rank)
+
+
+def all_gather_rows(local: torch.Tensor, n_rows: int, world: int, chunk: int = 256, group=None) -> torch.Tensor:
+    """Assemble the full [n_rows, ...] output from per-rank row-chunk results (row sharding).
+    Ranks may hold different row counts; results are padded to the largest for the collective."""
+    counts = [sum(b - a for a, b in row_chunks(n_rows, world, r, chunk)) for r in range(world)]
+    pad = max(counts)
+    buf = local.new_zeros((pad,) + tuple(local.shape[1:]))
+    buf[: local.shape[0]] = local
+    parts = [torch.empty_like(buf) for _ in range(world)]
+    dist.all_gather(parts, buf, group=group)
+    out = local.new_empty((n_rows,) + tuple(local.shape[1:]))
+    for r in range(world):
+        out[rows_of(row_chunks(n_rows, world, r, chunk), device=local.device)] = parts[r][: counts[r]]
+    return out
+
+
+def all_gather_heads(local: torch.Tensor, n_heads: int, world: int, group=None) -> torch.Tensor:
+    """Assemble [T, n_heads, D] from per-rank head slices [T, h_r, D] (head sharding)."""
+    sizes = [head_range(n_heads, world, r) for r in range(world)]
+    pad = max(b - a for a, b in sizes)
+    buf = local.new_zeros((local.shape[0], pad, local.shape[2]))
+    buf[:, : local.shape[1]] = local
+    parts = [torch.empty_like(buf) for _ in range(world)]
+    dist.all_gather(parts, buf.contiguous(), group=group)
+    return torch.cat([parts[r][:, : b - a] for r, (a, b) in enumerate(sizes)], dim=1)
+
+
+def all_gather_batch(local: torch.Tensor, batch: int, world: int, group=None) -> torch.Tensor:
+    """Assemble [batch, ...] decode outputs from contiguous per-rank slices."""
+    sizes = [batch_range(batch, world, r) for r in range(world)]
+    pad = max(b - a for a, b in sizes)
+    buf = local.new_zeros((pad,) + tuple(local.shape[1:]))
+    buf[: local.shape[0]] = local
+    parts = [torch.empty_like(buf) for _ in range(world)]
+    dist.all_gather(parts, buf, group=group)
+    return torch.cat([parts[r][: b - a] for r, (a, b) in enumerate(sizes)], dim=0)
