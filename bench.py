@@ -156,6 +156,78 @@ def run_reference(args, rank):
     }))
 
 
+def _time_ms(fn, iters, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def extra_measurements(dev, peaks):
+    """The other two parts of the path at their BASELINE shapes, device-resident, rank 0 only:
+    sparse MLA prefill (32768 tokens, 128 heads, 2048 selected keys, bf16) and one decode step
+    (batch 64, context 131072, paged FP8 caches, 64 indexer heads, top-k 2048, 128 heads)."""
+    from llmdivedeep_b200 import layer, ops
+    fp8 = torch.float8_e4m3fn
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(7)
+    # ---- sparse MLA prefill ---------------------------------------------------------
+    T = S = 32768
+    H, K = 128, TOPK
+    q = torch.randn(T, H, 576, device=dev, dtype=torch.bfloat16, generator=g)
+    kv = torch.randn(S, 576, device=dev, dtype=torch.bfloat16, generator=g)
+    idx = torch.empty(T, K, dtype=torch.int32, device=dev)
+    for t0 in range(0, T, 4096):                      # uniform positions <= t (drawn with replacement)
+        pos = torch.arange(t0, t0 + 4096, device=dev).unsqueeze(1) + 1
+        idx[t0:t0 + 4096] = (torch.rand(4096, K, device=dev, generator=g) * pos).int().clamp_max(S - 1)
+    idx[torch.arange(T, device=dev).unsqueeze(1) < torch.arange(K, device=dev).unsqueeze(0)] = -1
+    o = torch.empty(T, H, 512, dtype=torch.bfloat16, device=dev)
+    ms = _time_ms(lambda: ops.sparse_mla_prefill(q, kv, idx, 192 ** -0.5, out=o), iters=3, warm=1)
+    flops = 2.0 * H * (576 + 512) * float((idx >= 0).sum().item())
+    out["sparse_mla_prefill"] = {
+        "workload": "32768 tokens x 128 heads, qk 576 / v 512, 2048 selected keys per token (all keys <= t for t < 2048), bf16",
+        "ms": ms, "tokens_per_s": T / ms * 1e3, "tflops_algorithmic": flops / ms / 1e9,
+        "frac_of_bf16_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"],
+        "note": "positions drawn with replacement (timing only); the kernel computes Q.K^T twice per token (one CTA per V half)"}
+    del q, kv, idx, o
+    torch.cuda.empty_cache()
+    # ---- one decode step --------------------------------------------------------------
+    B, CTX = 64, 131072
+    P = CTX // 64
+    n_rows = B * P * 64
+    kcache = torch.randint(0, 120, (n_rows, 128), device=dev, dtype=torch.uint8, generator=g).view(fp8)
+    kscale = torch.rand(n_rows, device=dev, generator=g) * 0.01 + 0.001
+    table = torch.randperm(B * P, device=dev, generator=g).int().view(B, P)
+    ctx = torch.full((B,), CTX, dtype=torch.int32, device=dev)
+    q8 = (torch.randn(B, HEADS, DIM, device=dev, generator=g) * 50).to(fp8)
+    w = torch.randn(B, HEADS, device=dev, generator=g) / 8
+    latent = torch.randint(0, 120, (n_rows, 656), device=dev, dtype=torch.uint8, generator=g)
+    latent[:, 512:528] = torch.full((4,), 0.01, device=dev).view(torch.uint8).repeat(n_rows, 1)
+    latent[:, 528:] = torch.randn(n_rows, 64, device=dev, generator=g).to(torch.bfloat16).view(torch.uint8)
+    qd = torch.randn(B, 128, 576, device=dev, dtype=torch.bfloat16, generator=g)
+    dws = layer.DecodeWorkspace(B, 128, CTX, TOPK, dev)
+    step = lambda: layer.dsa_decode_step(q8, w, kcache, kscale, table, ctx, qd, latent, 192 ** -0.5, dws)
+    t_all = _time_ms(step, iters=10)
+    t_idx = _time_ms(lambda: ops.fp8_paged_mqa_logits(q8, w, kcache, kscale, table, ctx, CTX, out=dws.logits), iters=10)
+    t_top = _time_ms(lambda: ops.topk_select(dws.logits, TOPK, None, ctx, out=dws.idx), iters=10)
+    t_mla = _time_ms(lambda: ops.sparse_mla_decode_paged(qd, latent, table, dws.idx, 192 ** -0.5, CTX, out=dws.out), iters=10)
+    ops.check_status(dev)
+    scan_bytes = B * CTX * 132.0
+    out["decode_step"] = {
+        "workload": "batch 64, context 131072, 64-token pages in random order, FP8 caches, 64 indexer heads, top-k 2048, 128 heads",
+        "us_per_step": t_all * 1e3, "indexer_us": t_idx * 1e3, "topk_us": t_top * 1e3, "sparse_mla_us": t_mla * 1e3,
+        "indexer_gbs": scan_bytes / t_idx / 1e6, "indexer_frac_of_hbm": scan_bytes / t_idx / 1e6 / peaks["hbm_gbs"],
+        "sparse_mla_gather_gbs": B * TOPK * 656.0 / t_mla / 1e6,
+        "lower_bound_us": (scan_bytes + 2 * B * CTX * 4 + B * TOPK * 656.0) / peaks["hbm_gbs"] / 1e3}
+    return out
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -171,6 +243,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the secondary measurements (sparse MLA prefill, decode step)")
     ap.add_argument("--rows", type=int, default=T_ROWS,
                     help="query rows per step; anything but 4096 is a reduced case for profiler captures, not a bench value")
     args = ap.parse_args()
@@ -306,6 +380,10 @@ def main():
                     "topk_select_gbs": topk_bytes / (topk_ms * 1e-3) / 1e9,
                     "topk_select_frac_of_hbm": topk_bytes / (topk_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     }
+    if not args.no_extra and args.rows == 4096:
+        del sets, host_sets, dev_in, ws, logits
+        torch.cuda.empty_cache()
+        line["extra"] = extra_measurements(dev, peaks)
     if not args.no_cpu_baseline:
         rows = 512
         cpu_port_rows_per_s(16)
