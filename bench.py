@@ -216,7 +216,7 @@ def extra_measurements(dev, peaks):
     t_all = _time_ms(step, iters=10)
     t_idx = _time_ms(lambda: ops.fp8_paged_mqa_logits(q8, w, kcache, kscale, table, ctx, CTX, out=dws.logits), iters=10)
     t_top = _time_ms(lambda: ops.topk_select(dws.logits, TOPK, None, ctx, out=dws.idx), iters=10)
-    t_mla = _time_ms(lambda: ops.sparse_mla_decode_paged(qd, latent, table, dws.idx, 192 ** -0.5, CTX, out=dws.out), iters=10)
+    t_mla = _time_ms(lambda: ops.sparse_mla_decode_paged(qd, latent, table, dws.idx, 192 ** -0.5, CTX, out=dws.out, workspace=dws.mla_ws), iters=10)
     ops.check_status(dev)
     scan_bytes = B * CTX * 132.0
     out["decode_step"] = {

@@ -103,7 +103,7 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_fp8, const float* k_scale,
  * sparse-MLA kernel of its own.
  *   q_bf16 [T, H, 576] bf16; kv_bf16 [S_kv, 576] bf16; idx [T, K] int32 positions
  *   into kv (negative = empty; >= S_kv is skipped and sets status 2);
- *   out_bf16 [T, H, 512] bf16.  All contiguous and 16-byte aligned.  Any H >= 1
+ *   out_bf16 [T, H, 512] bf16.  All contiguous and 16-byte aligned.  K <= 2048.  Any H >= 1
  *   (heads are processed in groups of 128). */
 int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_t* idx, void* out_bf16, int T, int H,
                            int S_kv, int K, float scale, int32_t* status, void* stream);
@@ -115,10 +115,16 @@ int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_
  * 512 e4m3 latent values, 4 fp32 scales (one per 128 values), 64 bf16 rope
  * values; latent = e4m3 * scale is rounded to bf16 before the tensor-core math.
  *   q_bf16 [B, H, 576]; cache [num_pages*64, 656] bytes; block_table
- *   [B, table_stride] int32; idx [B, K] int32; out_bf16 [B, H, 512]. */
+ *   [B, table_stride] int32; idx [B, K] int32 (K <= 2048); out_bf16 [B, H, 512].
+ * With few sequences the slot list of each is cut into parts that run on
+ * different SMs and are merged by a second kernel; that needs `workspace` of
+ * dsa_sparse_mla_decode_workspace_bytes(B, H, K) bytes (16-byte aligned).  With
+ * workspace NULL or too small the call still works, one part per sequence. */
+size_t dsa_sparse_mla_decode_workspace_bytes(int B, int H, int K);
 int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int32_t* block_table,
                                 int64_t table_stride, const int32_t* idx, void* out_bf16, int B, int H, int K,
-                                int num_pages, int max_ctx, float scale, int32_t* status, void* stream);
+                                int num_pages, int max_ctx, float scale, void* workspace, size_t workspace_bytes,
+                                int32_t* status, void* stream);
 
 /* dsa_indexer_topk without a caller-supplied workspace.  No counterpart in the
  * reference: it exists for hosts that cannot allocate device memory at the call

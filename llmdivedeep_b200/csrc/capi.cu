@@ -53,7 +53,9 @@ int sparse_mla_prefill_launch(const void* q, const void* kv, const int32_t* idx,
                               int K, float scale, int32_t* status, cudaStream_t stream);
 int sparse_mla_decode_launch(const void* q, const void* cache, const int32_t* block_table, int64_t table_stride,
                              const int32_t* idx, void* out, int B, int H, int K, int num_pages, int max_ctx,
-                             float scale, int32_t* status, cudaStream_t stream);
+                             float scale, void* workspace, size_t workspace_bytes, int32_t* status,
+                             cudaStream_t stream);
+size_t mla_decode_workspace_bytes(int B, int H, int K);
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -134,13 +136,15 @@ int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_
     return set_error(DSA_ERR_ALIGN, "sparse_mla_prefill: q, kv and out must be 16-byte aligned");
   if ((int64_t)T * H > 0x7fffffffLL || T > 0x7fffffff / 2) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: T*H too large");
   if (H > 128 * 65535) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: too many heads");
+  if (K > 2048) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: K (%d) exceeds 2048 selected keys per query", K);
   return sparse_mla_prefill_launch(q_bf16, kv_bf16, idx, out_bf16, T, H, S_kv, K, scale, status,
                                    static_cast<cudaStream_t>(stream));
 }
 
 int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int32_t* block_table,
                                 int64_t table_stride, const int32_t* idx, void* out_bf16, int B, int H, int K,
-                                int num_pages, int max_ctx, float scale, int32_t* status, void* stream) {
+                                int num_pages, int max_ctx, float scale, void* workspace, size_t workspace_bytes,
+                                int32_t* status, void* stream) {
   g_err[0] = 0;
   if (B < 0 || H < 0 || K < 0 || num_pages < 0 || max_ctx < 0)
     return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: negative size");
@@ -151,10 +155,18 @@ int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int
     return set_error(DSA_ERR_ALIGN, "sparse_mla_decode_paged: q, cache and out must be 16-byte aligned");
   if (table_stride * 64 < max_ctx)
     return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: block table row shorter than max_ctx");
+  if (K > 2048) return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: K (%d) exceeds 2048 selected keys per query", K);
   if ((int64_t)num_pages * 64 > 0x7fffffffLL || (int64_t)B * H > 0x7fffffffLL)
     return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: problem too large");
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return set_error(DSA_ERR_WORKSPACE, "sparse_mla_decode_paged: workspace must be 16-byte aligned");
   return sparse_mla_decode_launch(q_bf16, cache, block_table, table_stride, idx, out_bf16, B, H, K, num_pages,
-                                  max_ctx, scale, status, static_cast<cudaStream_t>(stream));
+                                  max_ctx, scale, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+size_t dsa_sparse_mla_decode_workspace_bytes(int B, int H, int K) {
+  if (B <= 0 || H <= 0 || K <= 0) return 0;
+  return mla_decode_workspace_bytes(B, H, K);
 }
 
 static const int kMinChunkRows = 256;

@@ -34,19 +34,25 @@ namespace dsa {
 constexpr int kMlaDqk = 576;
 constexpr int kMlaDv = 512;
 constexpr int kMlaDvHalf = 256;
-constexpr int kMlaBlk = 64;                       // keys per block
+#ifndef DSA_MLA_BLK
+#define DSA_MLA_BLK 64
+#define DSA_MLA_BUFS 1
+#endif
+constexpr int kMlaBlk = DSA_MLA_BLK;              // keys per block
+constexpr int kMlaBufs = DSA_MLA_BUFS;            // KV buffers in shared memory (Q leaves room for 73.7 KB)
 constexpr int kMlaPanels = kMlaDqk / 64;          // 9 panels of 64 dims (128 bytes)
 constexpr int kMlaQPanelBytes = 128 * 128;        // 128 heads x 128 B
-constexpr int kMlaKPanelBytes = kMlaBlk * 128;    // 64 keys x 128 B
+constexpr int kMlaKPanelBytes = kMlaBlk * 128;    // 32 keys x 128 B
 constexpr int kMlaQBytes = kMlaPanels * kMlaQPanelBytes;   // 147456
-constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;   // 73728
+constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;   // 36864 per buffer
 constexpr int kMlaThreads = 288;
 constexpr int kMlaGatherThreads = 128;
-constexpr int kMlaSmemBytes = 1024 + kMlaQBytes + kMlaKBytes + 1024;
+constexpr int kMlaMaxK = 2048;                    // selected slots per query (row ids staged in shared memory)
+constexpr int kMlaSmemBytes = 1024 + kMlaQBytes + kMlaBufs * kMlaKBytes + 1024 + kMlaMaxK * 4;
 constexpr int kLatentTokenBytes = 656;            // 512 e4m3 + 4 fp32 scales + 64 bf16 rope
 constexpr int kLatentPage = 64;
 // tensor-memory columns
-constexpr uint32_t kColO = 0, kColS = 256, kColP = 320, kMlaTmemCols = 512;
+constexpr uint32_t kColO = 0, kColS = 256, kColP = kColS + 2 * kMlaBlk, kMlaTmemCols = 512;   // S: 2 x Blk, P: 2 x Blk/2 columns
 
 struct MlaArgs {
   const __nv_bfloat16* kv;        // prefill: [S_kv, 576] bf16
@@ -60,6 +66,9 @@ struct MlaArgs {
   int num_phys_rows;              // decode: rows of the cache
   float scale_log2e;              // softmax scale * log2(e)
   int* status;
+  int n_split;                    // > 1: each query's slot list is cut into n_split parts (decode with few queries)
+  float* part_o;                  // [T * n_split, H, 512] fp32 normalised partial outputs
+  float* part_lse;                // [T * n_split, H] log2-sum-exp of each part (-inf = empty part)
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -80,34 +89,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return r;
 }
 
-// Gather one block of 64 selected rows into the nine swizzled panels.  Thread g of 128.
+// Gather one block of selected rows into the nine swizzled panels of a buffer.  Thread g of 128.
+// rows_s: the block's row ids (prefill: kv row; decode: physical cache row), -1 = empty slot.
 template <bool FP8_PAGED>
-__device__ __forceinline__ void gather_block(const MlaArgs& a, int t, const int32_t* __restrict__ idx_blk, int n_in_blk,
-                                             uint8_t* kv_s, uint8_t* valid_s, int g) {
-  // row ids (prefill: kv row; decode: physical cache row), -1 when the slot is empty / out of range
-  __shared__ int rows_s[kMlaBlk];
-  if (g < kMlaBlk) {
-    int r = -1;
-    if (g < n_in_blk) {
-      const int pos = idx_blk[g];
-      if (pos >= 0) {
-        if (pos >= a.S_kv) {
-          if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
-        } else if constexpr (!FP8_PAGED) {
-          r = pos;
-        } else {
-          const int phys = a.block_table[(int64_t)t * a.table_stride + pos / kLatentPage];
-          if (phys >= 0 && (int64_t)(phys + 1) * kLatentPage <= a.num_phys_rows) r = phys * kLatentPage + pos % kLatentPage;
-          else if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
-        }
-      }
-    }
-    rows_s[g] = r;
-    valid_s[g] = r >= 0;
-  }
-  named_bar_sync(1, kMlaGatherThreads);
+__device__ __forceinline__ void gather_block(const MlaArgs& a, const int* __restrict__ rows_s, uint8_t* kv_s, int g) {
   if constexpr (!FP8_PAGED) {
-    // 64 rows x 72 chunks of 16 bytes
+    // rows x 72 chunks of 16 bytes
 #pragma unroll 4
     for (int q = g; q < kMlaBlk * 72; q += kMlaGatherThreads) {
       const int r = q / 72, cc = q - r * 72;
@@ -118,16 +105,31 @@ __device__ __forceinline__ void gather_block(const MlaArgs& a, int t, const int3
     }
     cp_async_wait_all();
   } else {
-    // latent: 64 rows x 32 chunks of 16 e4m3 -> two 16-byte bf16 chunks each; rope: 64 rows x 8 chunks
-    for (int q = g; q < kMlaBlk * 32; q += kMlaGatherThreads) {
-      const int r = q >> 5, cc = q & 31;               // cc: 16-element chunk of the 512 latent dims
-      const int row = rows_s[r];
-      uint4 o0 = make_uint4(0, 0, 0, 0), o1 = o0;
-      if (row >= 0) {
-        const uint8_t* rec = a.cache + (int64_t)row * kLatentTokenBytes;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rec + cc * 16));
-        const float sc = __ldg(reinterpret_cast<const float*>(rec + kMlaDv) + (cc >> 3));
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    // latent: rows x 32 chunks of 16 e4m3 -> two 16-byte bf16 chunks each; rope: rows x 8 chunks
+    // all loads of a batch are issued before the first use, so their latencies overlap
+    constexpr int kBatch = 8;
+    static_assert((kMlaBlk * 32) % (kMlaGatherThreads * kBatch) == 0, "latent chunks per thread must be a multiple of the batch");
+    for (int q0 = g; q0 < kMlaBlk * 32; q0 += kMlaGatherThreads * kBatch) {
+      uint4 raw[kBatch];
+      float sc[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int q = q0 + u * kMlaGatherThreads;
+        const int r = q >> 5, cc = q & 31;           // cc: 16-element chunk of the 512 latent dims
+        const int row = rows_s[r];
+        raw[u] = make_uint4(0, 0, 0, 0);
+        sc[u] = 0.f;
+        if (row >= 0) {
+          const uint8_t* rec = a.cache + (int64_t)row * kLatentTokenBytes;
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(rec + cc * 16));
+          sc[u] = __ldg(reinterpret_cast<const float*>(rec + kMlaDv) + (cc >> 3));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int q = q0 + u * kMlaGatherThreads;
+        const int r = q >> 5, cc = q & 31;
+        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
         uint32_t outw[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -136,24 +138,32 @@ __device__ __forceinline__ void gather_block(const MlaArgs& a, int t, const int3
             const __nv_fp8x2_storage_t pr = static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * hh)) & 0xffffu);
             const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3);
             const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-            outw[i * 2 + hh] = pack_bf16x2(f.x * sc, f.y * sc);
+            outw[i * 2 + hh] = pack_bf16x2(f.x * sc[u], f.y * sc[u]);
           }
         }
-        o0 = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-        o1 = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+        const int d0 = cc * 16;                        // first latent dim of this chunk
+        const int p = d0 >> 6, c = (d0 & 63) >> 3;     // panel, 16-byte chunk inside the 128-byte row (even)
+        uint8_t* base = kv_s + p * kMlaKPanelBytes + r * 128;
+        *reinterpret_cast<uint4*>(base + ((c ^ (r & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+        *reinterpret_cast<uint4*>(base + (((c + 1) ^ (r & 7)) << 4)) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
       }
-      const int d0 = cc * 16;                          // first latent dim of this chunk
-      const int p = d0 >> 6, c = (d0 & 63) >> 3;       // panel, 16-byte chunk inside the 128-byte row (even)
-      uint8_t* base = kv_s + p * kMlaKPanelBytes + r * 128;
-      *reinterpret_cast<uint4*>(base + ((c ^ (r & 7)) << 4)) = o0;
-      *reinterpret_cast<uint4*>(base + (((c + 1) ^ (r & 7)) << 4)) = o1;
     }
-    for (int q = g; q < kMlaBlk * 8; q += kMlaGatherThreads) {
-      const int r = q >> 3, c = q & 7;
-      const int row = rows_s[r];
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row >= 0) v = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)row * kLatentTokenBytes + kMlaDv + 16) + c);
-      *reinterpret_cast<uint4*>(kv_s + 8 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+    {
+      constexpr int kRope = kMlaBlk * 8 / kMlaGatherThreads;     // rope chunks per thread
+      uint4 v[kRope];
+#pragma unroll
+      for (int u = 0; u < kRope; ++u) {
+        const int q = g + u * kMlaGatherThreads;
+        const int row = rows_s[q >> 3];
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (row >= 0) v[u] = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)row * kLatentTokenBytes + kMlaDv + 16) + (q & 7));
+      }
+#pragma unroll
+      for (int u = 0; u < kRope; ++u) {
+        const int q = g + u * kMlaGatherThreads;
+        const int r = q >> 3, c = q & 7;
+        *reinterpret_cast<uint4*>(kv_s + 8 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = v[u];
+      }
     }
   }
   fence_async_smem();          // make the panel writes visible to the tensor core's reads
@@ -165,49 +175,78 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;                               // 9 panels [128 heads x 128 B]
-  uint8_t* kv_s = q_s + kMlaQBytes;                  // 9 panels [64 keys x 128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kMlaKBytes);
+  uint8_t* kv_s = q_s + kMlaQBytes;                  // 2 buffers x 9 panels [32 keys x 128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kMlaBufs * kMlaKBytes);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_free = bars + 2;
-  uint64_t* s_full = bars + 3;
-  uint64_t* p_full = bars + 4;
-  uint64_t* o_final = bars + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* o_final = bars + 1;
+  uint64_t* kv_full = bars + 2;                      // [2] gather -> MMA
+  uint64_t* kv_free = bars + 4;                      // [2] P.V of the block finished: its KV buffer is free
+  uint64_t* s_full = bars + 6;                       // [2] MMA -> softmax
+  uint64_t* p_full = bars + 8;                       // [2] softmax -> MMA
+  uint64_t* pv_done = bars + 10;                     // [2] P.V of block j finished: O is quiescent
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_s = const_cast<int*>(abort_flag) + 1;
-  uint8_t* valid_s = reinterpret_cast<uint8_t*>(last_s + 1);   // 64 flags of the current block
+  int* rows_all = reinterpret_cast<int*>(kv_s + kMlaBufs * kMlaKBytes + 1024);   // [kMlaMaxK] row id per slot, -1 = empty
 
-  const int t = blockIdx.x, vhalf = blockIdx.y, hg = blockIdx.z;
+  const int t = blockIdx.x / a.n_split, split = blockIdx.x % a.n_split, vhalf = blockIdx.y, hg = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int32_t* idx_row = a.idx + (int64_t)t * a.K;
+  const int k_per = ((a.K + a.n_split - 1) / a.n_split + kMlaBlk - 1) / kMlaBlk * kMlaBlk;   // slots per part
+  const int k_lo = min(a.K, split * k_per), k_cnt = min(a.K, k_lo + k_per) - k_lo;
+  const int32_t* idx_row = a.idx + (int64_t)t * a.K + k_lo;
   const int heads_here = min(128, a.H - hg * 128);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(kv_full, kMlaGatherThreads);
-    mbar_init(kv_free, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
     mbar_init(o_final, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&kv_full[b], kMlaGatherThreads);
+      mbar_init(&kv_free[b], 1);
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], 128);
+      mbar_init(&pv_done[b], 1);
+    }
     *abort_flag = 0;
     *last_s = -1;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
   }
   __syncthreads();
-  {  // last non-empty slot of this row decides how many 64-key blocks there are
+  {  // translate every slot to a row id once; the last non-empty slot decides the number of key blocks
     int last = -1;
-    for (int j = threadIdx.x; j < a.K; j += kMlaThreads)
-      if (idx_row[j] >= 0) last = j;
+    const int k_pad = (k_cnt + kMlaBlk - 1) / kMlaBlk * kMlaBlk;
+    for (int j = threadIdx.x; j < k_pad; j += kMlaThreads) {
+      int r = -1;
+      const int pos = j < k_cnt ? idx_row[j] : -1;
+      if (pos >= 0) {
+        if (pos >= a.S_kv) {
+          if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+        } else if constexpr (!FP8_PAGED) {
+          r = pos;
+        } else {
+          const int phys = a.block_table[(int64_t)t * a.table_stride + pos / kLatentPage];
+          if (phys >= 0 && (int64_t)(phys + 1) * kLatentPage <= a.num_phys_rows) r = phys * kLatentPage + pos % kLatentPage;
+          else if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+        }
+      }
+      rows_all[j] = r;
+      if (r >= 0) last = j;
+    }
     if (last >= 0) atomicMax(last_s, last);
   }
   __syncthreads();
   const int nblk = (*last_s + kMlaBlk) / kMlaBlk;
-  if (nblk == 0) {   // nothing selected: the output row is zero
+  if (nblk == 0) {   // nothing selected: the output row is zero (a part: weight zero in the combine)
     if (threadIdx.x < 128 && threadIdx.x < heads_here) {
-      uint4* o = reinterpret_cast<uint4*>(a.out + ((int64_t)t * a.H + hg * 128 + threadIdx.x) * kMlaDv + vhalf * kMlaDvHalf);
-      for (int c = 0; c < kMlaDvHalf * 2 / 16; ++c) o[c] = make_uint4(0, 0, 0, 0);
+      if (a.n_split == 1) {
+        uint4* o = reinterpret_cast<uint4*>(a.out + ((int64_t)t * a.H + hg * 128 + threadIdx.x) * kMlaDv + vhalf * kMlaDvHalf);
+        for (int c = 0; c < kMlaDvHalf * 2 / 16; ++c) o[c] = make_uint4(0, 0, 0, 0);
+      } else {
+        const int64_t prow = (int64_t)blockIdx.x * a.H + hg * 128 + threadIdx.x;
+        float4* o = reinterpret_cast<float4*>(a.part_o + prow * kMlaDv + vhalf * kMlaDvHalf);
+        for (int c = 0; c < kMlaDvHalf / 4; ++c) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (vhalf == 0) a.part_lse[prow] = -CUDART_INF_F;
+      }
     }
     return;
   }
@@ -222,6 +261,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
 
   if (warp == 4) {
     // ------------------------------- MMA issuer -------------------------------
+    // Issue order: QK(0), then per block j: QK(j+1) (so the next scores are computed while
+    // the softmax of block j runs), wait for P(j), PV(j).  MMAs complete in issue order.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(1, 1, 0, 0, 128, kMlaBlk);
       constexpr uint32_t idesc_pv = umma_idesc(1, 1, 0, 1, 128, kMlaDvHalf);
@@ -229,38 +270,56 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
       for (int p = 0; p < kMlaPanels; ++p)
         tma_load_2d(q_s + p * kMlaQPanelBytes, &tmap_q, p * 128, t * a.H + hg * 128, q_full);
       bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
-      const uint64_t vdesc = umma_smem_desc(smem_u32(kv_s + vhalf * 4 * kMlaKPanelBytes), kMlaKPanelBytes, 1024, kSwz128);
-      for (int j = 0; j < nblk && ok; ++j) {
-        ok = mbar_wait(kv_full, j & 1, abort_flag, a.status);
-        if (!ok) break;
+      auto issue_qk = [&](int j) -> bool {
+        const int b = j & 1, kvb = j % kMlaBufs;
+        if (!mbar_wait(&kv_full[kvb], (j / kMlaBufs) & 1, abort_flag, a.status)) return false;
         tc_fence_after();
+        const uint8_t* kb = kv_s + kvb * kMlaKBytes;
 #pragma unroll 1
         for (int p = 0; p < kMlaPanels; ++p) {
           const uint64_t qd = umma_smem_desc(smem_u32(q_s + p * kMlaQPanelBytes), 16, 1024, kSwz128);
-          const uint64_t kd = umma_smem_desc(smem_u32(kv_s + p * kMlaKPanelBytes), 16, 1024, kSwz128);
+          const uint64_t kd = umma_smem_desc(smem_u32(kb + p * kMlaKPanelBytes), 16, 1024, kSwz128);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma_f16_ss(tmem + kColS, qd + 2 * ks, kd + 2 * ks, idesc_qk, (p | ks) != 0);
+            umma_f16_ss(tmem + kColS + b * kMlaBlk, qd + 2 * ks, kd + 2 * ks, idesc_qk, (p | ks) != 0);
         }
-        umma_commit(s_full);
-        ok = mbar_wait(p_full, j & 1, abort_flag, a.status);
+        umma_commit(&s_full[b]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int b = j & 1, kvb = j % kMlaBufs;
+        // next scores first only if their keys have already landed; never stall P.V behind a gather
+        bool qk_done = j + 1 >= nblk;
+        if (!qk_done && kMlaBufs > 1 && mbar_try_wait(&kv_full[(j + 1) % kMlaBufs], ((j + 1) / kMlaBufs) & 1)) {
+          ok = issue_qk(j + 1);
+          qk_done = true;
+        }
+        if (!ok) break;
+        ok = mbar_wait(&p_full[b], (j >> 1) & 1, abort_flag, a.status);
         if (!ok) break;
         tc_fence_after();
+        const uint64_t vdesc = umma_smem_desc(smem_u32(kv_s + kvb * kMlaKBytes + vhalf * 4 * kMlaKPanelBytes),
+                                              kMlaKPanelBytes, 1024, kSwz128);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)      // 16 keys per step: 16 rows x 128 B further into each panel
-          umma_f16_ts(tmem + kColO, tmem + kColP + 8 * ks, vdesc + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
-        umma_commit(kv_free);
+        for (int ks = 0; ks < kMlaBlk / 16; ++ks)     // 16 keys per step: 16 rows x 128 B further into each panel
+          umma_f16_ts(tmem + kColO, tmem + kColP + b * (kMlaBlk / 2) + 8 * ks, vdesc + ks * (2048 >> 4), idesc_pv,
+                      (j | ks) != 0);
+        umma_commit(&kv_free[kvb]);
+        umma_commit(&pv_done[b]);
         if (j == nblk - 1) umma_commit(o_final);
+        if (!qk_done) ok = issue_qk(j + 1);
       }
     }
   } else if (warp >= 5) {
     // --------------------------------- gather ---------------------------------
     const int g = threadIdx.x - 160;
     for (int j = 0; j < nblk; ++j) {
-      mbar_wait(kv_free, (j & 1) ^ 1, abort_flag, a.status);
-      gather_block<FP8_PAGED>(a, t, idx_row + j * kMlaBlk, min(kMlaBlk, a.K - j * kMlaBlk), kv_s, valid_s, g);
-      mbar_arrive(kv_full);
-      if (*abort_flag) break;       // uniform: checked after the gather threads' own barrier
+      const int kvb = j % kMlaBufs;
+      mbar_wait(&kv_free[kvb], ((j / kMlaBufs) & 1) ^ 1, abort_flag, a.status);
+      gather_block<FP8_PAGED>(a, rows_all + j * kMlaBlk, kv_s + kvb * kMlaKBytes, g);
+      mbar_arrive(&kv_full[kvb]);
+      if (*abort_flag) break;
     }
   } else {
     // ------------------------- softmax and output (thread = head) -------------------------
@@ -269,19 +328,22 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
     float m = -CUDART_INF_F, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nblk; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, a.status));
+      const int b = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, a.status));
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[2][32];
-      tmem_ld32(t_row + kColS, sv[0]);
-      tmem_ld32(t_row + kColS + 32, sv[1]);
-      tmem_wait_ld();
-      float s[64];
-      float bmax = -CUDART_INF_F;
+      uint32_t sv[kMlaBlk];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float x = __uint_as_float(sv[i >> 5][i & 31]) * a.scale_log2e;
-        s[i] = valid_s[i] ? x : -CUDART_INF_F;
+      for (int c = 0; c < kMlaBlk; c += 32)
+        tmem_ld32(t_row + kColS + b * kMlaBlk + c, *reinterpret_cast<uint32_t(*)[32]>(sv + c));
+      tmem_wait_ld();
+      float s[kMlaBlk];
+      float bmax = -CUDART_INF_F;
+      const int* vrow = rows_all + j * kMlaBlk;
+#pragma unroll
+      for (int i = 0; i < kMlaBlk; ++i) {
+        const float x = __uint_as_float(sv[i]) * a.scale_log2e;
+        s[i] = vrow[i] >= 0 ? x : -CUDART_INF_F;
         bmax = fmaxf(bmax, s[i]);
       }
       const float m_new = fmaxf(m, bmax);
@@ -291,6 +353,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         if (grow) m = m_new;
         l *= alpha;
         if (j > 0) {
+          // O must be quiescent: P.V of the previous block has to be complete
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[b ^ 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < kMlaDvHalf; c += 32) {
             uint32_t ov[32];
@@ -303,31 +369,42 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         }
       }
       const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-      uint32_t pk[32];
+      uint32_t pk[kMlaBlk / 2];
       float psum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 64; i += 2) {
+      for (int i = 0; i < kMlaBlk; i += 2) {
         const float p0 = fast_exp2(s[i] - m_eff), p1 = fast_exp2(s[i + 1] - m_eff);
         psum += p0 + p1;
         pk[i >> 1] = pack_bf16x2(p0, p1);
       }
       l += psum;
-      tmem_st32(t_row + kColP, pk);
+#pragma unroll
+      for (int c = 0; c < kMlaBlk / 2; c += 16)
+        tmem_st16(t_row + kColP + b * (kMlaBlk / 2) + c, *reinterpret_cast<uint32_t(*)[16]>(pk + c));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[b]);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = a.out + ((int64_t)t * a.H + hg * 128 + row) * kMlaDv + vhalf * kMlaDvHalf;
+      const int64_t prow = (int64_t)blockIdx.x * a.H + hg * 128 + row;
+      if (a.n_split > 1 && vhalf == 0 && row < heads_here)
+        a.part_lse[prow] = l > 0.f ? m + log2f(l) : -CUDART_INF_F;
 #pragma unroll 1
       for (int c = 0; c < kMlaDvHalf; c += 32) {
         uint32_t ov[32];
         tmem_ld32(t_row + kColO + c, ov);
         tmem_wait_ld();
-        if (row < heads_here) {
+        if (row < heads_here && a.n_split > 1) {
+          float4* po = reinterpret_cast<float4*>(a.part_o + prow * kMlaDv + vhalf * kMlaDvHalf + c);
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            po[i >> 2] = make_float4(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv,
+                                     __uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+        } else if (row < heads_here) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 w;
@@ -350,6 +427,32 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
   }
 }
 
+// out[t,h,:] = sum_s 2^(lse_s - M) o_s / sum_s 2^(lse_s - M): merges the parts of a split slot list.
+__global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const MlaArgs a) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  float wgt[16];
+  float mx = -CUDART_INF_F, den = 0.f;
+  for (int sp = 0; sp < a.n_split; ++sp) {
+    wgt[sp] = a.part_lse[((int64_t)t * a.n_split + sp) * a.H + h];
+    mx = fmaxf(mx, wgt[sp]);
+  }
+  for (int sp = 0; sp < a.n_split; ++sp) {
+    wgt[sp] = (mx == -CUDART_INF_F) ? 0.f : exp2f(wgt[sp] - mx);
+    den += wgt[sp];
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const int d = threadIdx.x * 4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sp = 0; sp < a.n_split; ++sp) {
+    const float4 v = *reinterpret_cast<const float4*>(a.part_o + (((int64_t)t * a.n_split + sp) * a.H + h) * kMlaDv + d);
+    acc.x += wgt[sp] * v.x; acc.y += wgt[sp] * v.y; acc.z += wgt[sp] * v.z; acc.w += wgt[sp] * v.w;
+  }
+  uint2 o;
+  o.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+  o.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(a.out + ((int64_t)t * a.H + h) * kMlaDv + d) = o;
+}
+
 int make_tmap_2d_bytes(CUtensorMap* m, const void* base, uint64_t rows, uint64_t inner_bytes, uint64_t row_pitch,
                        uint32_t box_bytes, uint32_t box_rows);
 
@@ -362,8 +465,9 @@ static int launch_mla(const void* q, const MlaArgs& a, cudaStream_t stream) {
   auto kern = sparse_mla_kernel<FP8_PAGED>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes) != cudaSuccess)
     return set_error(DSA_ERR_CUDA, "sparse_mla: cannot raise dynamic shared memory to %d", kMlaSmemBytes);
-  const dim3 grid(a.T, 2, (a.H + 127) / 128);
+  const dim3 grid(a.T * a.n_split, 2, (a.H + 127) / 128);
   kern<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tq, a);
+  if (a.n_split > 1) sparse_mla_combine_kernel<<<dim3(a.T, a.H), 128, 0, stream>>>(a);
   return check_launch("sparse_mla");
 }
 
@@ -376,13 +480,36 @@ int sparse_mla_prefill_launch(const void* q, const void* kv, const int32_t* idx,
   a.T = T; a.H = H; a.K = K; a.S_kv = S_kv;
   a.scale_log2e = scale * 1.4426950408889634f;
   a.status = status;
+  a.n_split = 1;
   return launch_mla<false>(q, a, stream);
+}
+
+// With few queries (decode) one CTA pair per query leaves most SMs idle and walks 2048 slots
+// serially: cut the slot list into parts of >= 256 slots until the grid fills the GPU about 4 times.
+int mla_decode_splits(int B, int H, int K) {
+  const int ctas = B * 2 * ((H + 127) / 128);
+  int ns = 1;
+  while (ns < 8 && ctas * ns < 4 * sm_count() && K / (ns * 2) >= 256) ns *= 2;
+  return ns;
+}
+size_t mla_decode_workspace_bytes(int B, int H, int K) {
+  const int ns = mla_decode_splits(B, H, K);
+  if (ns <= 1) return 0;
+  return (size_t)B * ns * H * (kMlaDv + 1) * sizeof(float);
 }
 
 int sparse_mla_decode_launch(const void* q, const void* cache, const int32_t* block_table, int64_t table_stride,
                              const int32_t* idx, void* out, int B, int H, int K, int num_pages, int max_ctx,
-                             float scale, int32_t* status, cudaStream_t stream) {
+                             float scale, void* workspace, size_t workspace_bytes, int32_t* status,
+                             cudaStream_t stream) {
   MlaArgs a{};
+  a.n_split = mla_decode_splits(B, H, K);
+  if (a.n_split > 1 && workspace && workspace_bytes >= mla_decode_workspace_bytes(B, H, K)) {
+    a.part_o = static_cast<float*>(workspace);
+    a.part_lse = a.part_o + (size_t)B * a.n_split * H * kMlaDv;
+  } else {
+    a.n_split = 1;
+  }
   a.cache = static_cast<const uint8_t*>(cache);
   a.block_table = block_table;
   a.table_stride = table_stride;

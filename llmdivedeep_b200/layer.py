@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from . import ops
+from . import _lib, ops
 
 
 class SparseMLA(nn.Module):
@@ -51,6 +51,8 @@ class DecodeWorkspace:
         self.logits = torch.empty(batch, ld, dtype=torch.float32, device=device)
         self.idx = torch.empty(batch, topk, dtype=torch.int32, device=device)
         self.out = torch.empty(batch, heads, 512, dtype=torch.bfloat16, device=device)
+        need = _lib.load().dsa_sparse_mla_decode_workspace_bytes(batch, heads, min(topk, max_ctx))
+        self.mla_ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
         self.max_ctx, self.topk = max_ctx, topk
 
 
@@ -63,5 +65,6 @@ def dsa_decode_step(q_idx_fp8, w, kcache, kscale, block_table, ctx_len, q, laten
     logits = ops.fp8_paged_mqa_logits(q_idx_fp8, w, kcache, kscale, block_table, ctx_len, ws.max_ctx, out=ws.logits)
     k = min(ws.topk, ws.max_ctx)
     ops.topk_select(logits, k, None, ctx_len, out=ws.idx[:B])
-    ops.sparse_mla_decode_paged(q, latent_cache, block_table, ws.idx[:B], softmax_scale, ws.max_ctx, out=ws.out[:B])
+    ops.sparse_mla_decode_paged(q, latent_cache, block_table, ws.idx[:B], softmax_scale, ws.max_ctx, out=ws.out[:B],
+                                workspace=ws.mla_ws)
     return ws.idx[:B], ws.out[:B]

@@ -226,7 +226,7 @@ def sparse_mla_prefill(q, kv, idx, scale: float, out: Optional[torch.Tensor] = N
 
 
 def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: Optional[int] = None,
-                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode step over the paged FP8 latent cache.  q [B,H,576] bf16, cache uint8
     [num_pages*64, 656], block_table [B,P] int32, idx [B,K] int32 logical positions."""
     _need_cuda(q, cache, block_table, idx)
@@ -241,7 +241,11 @@ def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: O
     if out is None:
         out = torch.empty(B, H, 512, dtype=torch.bfloat16, device=q.device)
     lib = _lib.load()
+    if workspace is None:
+        need = lib.dsa_sparse_mla_decode_workspace_bytes(B, H, idx.shape[1])
+        workspace = _workspace(q.device, need) if need else None
     check(lib.dsa_sparse_mla_decode_paged(_ptr(q), _ptr(cache), _ptr(block_table), block_table.stride(0), _ptr(idx),
                                           _ptr(out), B, H, idx.shape[1], cache.shape[0] // 64, max_ctx, float(scale),
+                                          _ptr(workspace), workspace.numel() if workspace is not None else 0,
                                           _ptr(status_word(q.device)), _stream()))
     return out

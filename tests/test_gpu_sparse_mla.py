@@ -132,3 +132,24 @@ def test_decode_bad_page_is_flagged():
     ok[0, 192:] = -1
     table[0, 3] = 3
     check(out, O.sparse_mla_decode_paged(q.float(), cache, table, ok, 0.06, round_bf16=True))
+
+
+def test_decode_split_parts_match_the_single_part_path():
+    """Few sequences with long slot lists take the split path (parts merged by a second kernel);
+    a workspace too small for it forces the single-part path.  Both must agree."""
+    from llmdivedeep_b200 import _lib
+    B, H, P, K = 2, 128, 40, 2048
+    g = torch.Generator().manual_seed(77)
+    kv = torch.randn(B * P * 64, 576, generator=g).to(torch.bfloat16)
+    cache = O.pack_latent_cache(kv).cuda()
+    table = torch.randperm(B * P, generator=g).int().view(B, P).cuda()
+    idx = torch.stack([torch.randperm(P * 64, generator=g)[:K] for _ in range(B)]).int()
+    idx[1, 300:1500] = -1                                  # whole parts of sequence 1 are empty
+    idx = idx.cuda()
+    q = torch.randn(B, H, 576, generator=g).to(torch.bfloat16).cuda()
+    assert _lib.load().dsa_sparse_mla_decode_workspace_bytes(B, H, K) > 0
+    split = ops.sparse_mla_decode_paged(q, cache, table, idx, 0.06)
+    single = ops.sparse_mla_decode_paged(q, cache, table, idx, 0.06, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    ops.check_status("cuda")
+    assert float((split.float() - single.float()).abs().max()) <= 1e-2
+    check(split, O.sparse_mla_decode_paged(q.float().cpu(), cache.cpu(), table.cpu(), idx.cpu(), 0.06, round_bf16=True))
