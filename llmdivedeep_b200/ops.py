@@ -249,3 +249,79 @@ def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: O
                                           _ptr(workspace), workspace.numel() if workspace is not None else 0,
                                           _ptr(status_word(q.device)), _stream()))
     return out
+
+
+class HostIndexerPipeline:
+    """indexer_topk for inputs and outputs that live in (pinned) host memory.
+
+    The call is cut into chunks of query rows: while chunk i is scored on the compute stream,
+    chunk i+1's q / weights / windows travel host -> device on a copy stream and chunk i-1's
+    indices travel device -> host, so the PCIe time hides behind the kernels instead of adding
+    to them.  The keys (shared by every chunk) are copied first.  Device staging buffers are
+    allocated once per shape and reused."""
+
+    def __init__(self, T: int, S: int, H: int, D: int, k: int, device, chunks: int = 4, w_dtype=torch.float32):
+        self.T, self.S, self.H, self.D, self.k, self.device = T, S, H, D, min(k, S), torch.device(device)
+        rows = -(-T // chunks)
+        rows = max(256, -(-rows // 256) * 256)                # whole 256-row groups per chunk
+        self.bounds = [(a, min(T, a + rows)) for a in range(0, T, rows)]
+        dev = self.device
+        self.k_fp8 = torch.empty(S, D, dtype=FP8, device=dev)
+        self.k_scale = torch.empty(S, dtype=torch.float32, device=dev)
+        self.q = [torch.empty(rows, H, D, dtype=FP8, device=dev) for _ in range(2)]
+        self.w = [torch.empty(rows, H, dtype=w_dtype, device=dev) for _ in range(2)]
+        self.ks = [torch.empty(rows, dtype=torch.int32, device=dev) for _ in range(2)]
+        self.ke = [torch.empty(rows, dtype=torch.int32, device=dev) for _ in range(2)]
+        self.out = [torch.empty(rows, self.k, dtype=torch.int32, device=dev) for _ in range(2)]
+        lib = _lib.load()
+        self.ws = torch.empty(lib.dsa_indexer_topk_workspace_bytes(rows, S), dtype=torch.uint8, device=dev)
+        self.copy_in = torch.cuda.Stream(device=dev)
+        self.copy_out = torch.cuda.Stream(device=dev)
+
+    def __call__(self, q_host, k_host, k_scale_host, w_host, ks_host, ke_host, out_host) -> torch.Tensor:
+        """All arguments are host tensors (pinned for real overlap); out_host int32 [T, k]."""
+        main = torch.cuda.current_stream(self.device)
+        n = len(self.bounds)
+        in_ready = [torch.cuda.Event() for _ in range(n)]
+        computed = [torch.cuda.Event() for _ in range(n)]
+        drained = [torch.cuda.Event() for _ in range(n)]
+        self.copy_in.wait_stream(main)
+        self.copy_out.wait_stream(main)
+
+        def stage(i):          # enqueue the host -> device copies of chunk i (events it waits on are already recorded)
+            a, b = self.bounds[i]
+            s = i & 1
+            with torch.cuda.stream(self.copy_in):
+                if i == 0:
+                    self.k_fp8.copy_(k_host, non_blocking=True)
+                    self.k_scale.copy_(k_scale_host, non_blocking=True)
+                if i >= 2:
+                    self.copy_in.wait_event(computed[i - 2])     # staging slot free again
+                self.q[s][: b - a].copy_(q_host[a:b], non_blocking=True)
+                self.w[s][: b - a].copy_(w_host[a:b], non_blocking=True)
+                self.ke[s][: b - a].copy_(ke_host[a:b], non_blocking=True)
+                if ks_host is not None:
+                    self.ks[s][: b - a].copy_(ks_host[a:b], non_blocking=True)
+                else:
+                    self.ks[s].zero_()
+                in_ready[i].record(self.copy_in)
+
+        stage(0)
+        if n > 1:
+            stage(1)
+        for i, (a, b) in enumerate(self.bounds):
+            s = i & 1
+            main.wait_event(in_ready[i])
+            if i >= 2:
+                main.wait_event(drained[i - 2])                  # output slot copied out
+            indexer_topk(self.q[s][: b - a], self.k_fp8, self.k_scale, self.w[s][: b - a], self.ks[s][: b - a],
+                         self.ke[s][: b - a], self.k, workspace=self.ws, out=self.out[s][: b - a])
+            computed[i].record(main)
+            if i + 2 < n:
+                stage(i + 2)
+            with torch.cuda.stream(self.copy_out):
+                self.copy_out.wait_event(computed[i])
+                out_host[a:b].copy_(self.out[s][: b - a], non_blocking=True)
+                drained[i].record(self.copy_out)
+        main.wait_stream(self.copy_out)
+        return out_host

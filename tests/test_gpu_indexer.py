@@ -144,3 +144,20 @@ def test_full_size_linearity_property():
     assert float(((a + b)[fin] - c[fin]).abs().max()) <= 1e-5 * float(c[fin].abs().max())
     d = ops.fp8_mqa_logits(q8, (k8, ksc * 2), w, ks, ke)
     assert torch.equal(d[fin], a[fin] * 2)
+
+
+def test_host_pipeline_matches_device_call():
+    """Pinned-host inputs and outputs, chunked with copies on side streams: same indices, twice."""
+    T, S, K = 1500, 4096, 256
+    args = indexer_inputs(T, S, 64, 128, seed=31, window="random")
+    want = ops.indexer_topk(*to_dev(*args), K).cpu()
+    pipe = ops.HostIndexerPipeline(T, S, 64, 128, K, "cuda", chunks=3)
+    assert len(pipe.bounds) == 3
+    host = [t.pin_memory() for t in args]
+    out = torch.empty(T, K, dtype=torch.int32).pin_memory()
+    for _ in range(2):
+        out.fill_(-5)
+        pipe(*host, out)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    ops.check_status("cuda")
