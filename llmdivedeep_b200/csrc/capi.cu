@@ -107,8 +107,8 @@ int dsa_indexer_logits_paged(const void* q_fp8, const void* w, int w_dtype, cons
   if (table_stride * 64 < max_ctx)
     return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: block table row (%lld pages) shorter than max_ctx %d",
                      (long long)table_stride, max_ctx);
-  if (!aligned16(q_fp8) || !aligned16(kcache))
-    return set_error(DSA_ERR_ALIGN, "indexer_logits_paged: q_fp8 and kcache must be 16-byte aligned");
+  if (!aligned16(q_fp8) || !aligned16(kcache) || !aligned16(kscale))
+    return set_error(DSA_ERR_ALIGN, "indexer_logits_paged: q_fp8, kcache and kscale must be 16-byte aligned");
   if ((int64_t)num_pages * 64 > 0x7fffffffLL) return set_error(DSA_ERR_SHAPE, "indexer_logits_paged: cache too large");
   return indexer_logits_paged(q_fp8, w, w_dtype, kcache, kscale, block_table, table_stride, ctx_len, logits,
                               ld_logits, B, H, D, num_pages, max_ctx, status, static_cast<cudaStream_t>(stream));

@@ -59,7 +59,7 @@ struct IdxCfg {
   static constexpr int KSTEPS = D / 32;
   static constexpr int K_TILE_BYTES = kTileKeys * D;
   static constexpr int Q_TILE_BYTES = N * D;
-  static constexpr int STAGES = (QB == 1) ? 6 : 4;
+  static constexpr int STAGES = PAGED ? 10 : ((QB == 1) ? 6 : 4);
   static constexpr int TMEM_COLS = (2 * N < 32) ? 32 : 2 * N;
   static constexpr uint64_t SWZ = (D == 128) ? kSwz128 : kSwz64;
   static constexpr uint32_t SBO = 8 * D;                 // 8 rows of D bytes
@@ -69,7 +69,7 @@ struct IdxCfg {
   static constexpr int COLS_PER_WG = N / SPLIT;
   static constexpr int CH = 16;                          // columns per TMEM load
   static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * K_TILE_BYTES + 2 * QB * Q_TILE_BYTES +
-                                    2 * QB * N * 4 + 2 * NTOK * 8 + 256;
+                                    2 * QB * N * 4 + 2 * NTOK * 8 + 256 + (PAGED ? 4 * kChunkTiles * 4 : 0);
   static_assert(EPI == 2 || EPI == 4, "two or four epilogue warpgroups");
   static_assert(N % 16 == 0 && N >= 16 && N <= 256, "MMA N out of range");
   static_assert(COLS_PER_WG % H == 0 && COLS_PER_WG % CH == 0, "a warpgroup must own whole tokens");
@@ -215,6 +215,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   uint64_t* w_empty = w_full + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* pages_s = const_cast<int*>(abort_flag) + 1;            // paged: physical page of every page of the unit's chunk
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -246,24 +247,48 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 0 || (PAGED && warp == 3)) {
     // ------------------------------ TMA producer ------------------------------
+    // paged: warps 0 and 3 each take every other tile (the per-copy issue latency of two threads overlaps)
+    constexpr int PL = PAGED ? 2 : 1;
+    const int pidx = warp == 0 ? 0 : 1;
+    int* my_pages = pages_s + pidx * 2 * kChunkTiles;
     uint32_t it = 0, nu = 0;
+    PROF_DECL();
+    PROF_T0();
     for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
       int qb, nb, t_lo, t_hi;
       if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
       const int qs = nu & 1;
       bool ok = true;
-      if (lane == 0) {
+      if constexpr (PAGED) {
+        // the whole warp fetches the chunk's page ids at once (coalesced), so the issuing lane
+        // never waits on a dependent global load per tile
+        const int n_pages = (min(a.ke[qb], a.S) + kPageTokens - 1) / kPageTokens;
+        __syncwarp();
+        for (int i = lane; i < 2 * (t_hi - t_lo); i += 32) {
+          const int page = 2 * t_lo + i;
+          my_pages[i] = page < n_pages ? __ldg(a.block_table + (int64_t)qb * a.table_stride + page) : -2;
+        }
+        __syncwarp();
+      }
+      // Issuing a copy costs the issuing thread several hundred cycles of latency (barrier poll, expect_tx,
+      // copy), whatever its size.
+      if (lane == 0 && pidx == 0) {
         ok = mbar_wait(&q_empty[qs], ((nu >> 1) & 1) ^ 1, abort_flag, a.status);
         if (ok) {
           mbar_expect_tx(&q_full[qs], nb * C::Q_TILE_BYTES);
           for (int b = 0; b < nb; ++b)
             tma_load_2d(q_s + (qs * QB + b) * C::Q_TILE_BYTES, &tmap_q, 0, (qb * QB + b) * C::N, &q_full[qs]);
         }
+      }
+      if (lane == 0) {
         for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
+          if (int(it % PL) != pidx) continue;
           const int st = it % C::STAGES;
+          PROF_ADD(1);
           ok = mbar_wait(&k_empty[st], ((it / C::STAGES) & 1) ^ 1, abort_flag, a.status);
+          PROF_ADD(0);
           if (!ok) break;
           uint8_t* dst = k_s + st * C::K_TILE_BYTES;
           if constexpr (!PAGED) {
@@ -271,15 +296,13 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             tma_load_2d(dst, &tmap_k, 0, kt * kTileKeys, &k_full[st]);
           } else {
             // two 64-token pages per tile; a missing or out-of-range page is skipped
-            const int n_pages = (min(a.ke[qb], a.S) + kPageTokens - 1) / kPageTokens;
             int rows[2];
             uint32_t bytes = 0;
 #pragma unroll
             for (int p = 0; p < 2; ++p) {
-              const int page = kt * 2 + p;
               rows[p] = -1;
-              if (page < n_pages) {
-                const int phys = a.block_table[(int64_t)qb * a.table_stride + page];
+              const int phys = my_pages[2 * (kt - t_lo) + p];    // -2: beyond the sequence's last page
+              if (phys != -2) {
                 if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows) {
                   rows[p] = phys * kPageTokens;
                   bytes += C::K_TILE_BYTES / 2;
@@ -300,10 +323,12 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
       }
       ++nu;
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      it = __shfl_sync(0xffffffffu, it, 0);
+      ok = __all_sync(0xffffffffu, ok);
+      it = __shfl_sync(0xffffffffu, it, 0) ;
       if (!ok) break;
     }
+    PROF_ADD(2);
+    if (pidx == 0) PROF_STORE(12);
     // on abort, give copies already in flight a bounded chance to land
     if (lane == 0 && *abort_flag) {
       for (int st = 0; st < C::STAGES; ++st)
@@ -426,10 +451,17 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
       };
       const uint32_t ld32 = static_cast<uint32_t>(a.ld);
-      float kscale_next = load_kscale(t_lo);     // always one key tile ahead of the math
+      // k_scale is requested ahead of the math: one key tile for contiguous keys, four for the paged
+      // cache, where it takes two dependent loads (page id, then scale) and tiles are short
+      constexpr int AHEAD = PAGED ? 4 : 1;
+      float ksq[AHEAD];
+#pragma unroll
+      for (int i = 0; i < AHEAD; ++i) ksq[i] = load_kscale(min(t_lo + i, t_hi - 1));
       for (int kt = t_lo; kt < t_hi && ok; ++kt) {
-        const float kscale = kscale_next;
-        kscale_next = load_kscale(min(kt + 1, t_hi - 1));
+        const float kscale = ksq[0];
+#pragma unroll
+        for (int i = 0; i + 1 < AHEAD; ++i) ksq[i] = ksq[i + 1];
+        ksq[AHEAD - 1] = load_kscale(min(kt + AHEAD, t_hi - 1));
         for (int b = 0; b < nb; ++b, ++it2) {
           if (int(it2 & 1) != stage) continue;
           const int s = kt * kTileKeys + row;    // logical key position
@@ -520,19 +552,22 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // 2-D byte tensor [rows, inner_bytes] (row pitch in bytes) with a [box_rows, box_bytes] box whose
-// shared-memory image is swizzled by the box width (128 or 64 bytes).
+// shared-memory image is swizzled by the box width (128 or 64 bytes).  The map is declared with
+// 4-byte elements (every size here is a multiple of 4), so the x coordinate of a copy counts
+// 4-byte units; the swizzle works on 16-byte chunks and does not depend on the element type.
 int make_tmap_2d_bytes(CUtensorMap* m, const void* base, uint64_t rows, uint64_t inner_bytes, uint64_t row_pitch,
                        uint32_t box_bytes, uint32_t box_rows) {
   auto fn = encode_fn();
   if (!fn) return set_error(DSA_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
-  cuuint64_t dims[2] = {inner_bytes, rows};
+  if ((inner_bytes | box_bytes) & 3) return set_error(DSA_ERR_SHAPE, "tensor map: sizes must be multiples of 4 bytes");
+  cuuint64_t dims[2] = {inner_bytes / 4, rows};
   cuuint64_t strides[1] = {row_pitch};
-  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t box[2] = {box_bytes / 4, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapSwizzle sw = box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                         : box_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
                                            : CU_TENSOR_MAP_SWIZZLE_NONE;
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(DSA_ERR_CUDA, "cuTensorMapEncodeTiled failed (code %d)", (int)r);

@@ -268,7 +268,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
       constexpr uint32_t idesc_pv = umma_idesc(1, 1, 0, 1, 128, kMlaDvHalf);
       mbar_expect_tx(q_full, kMlaQBytes);
       for (int p = 0; p < kMlaPanels; ++p)
-        tma_load_2d(q_s + p * kMlaQPanelBytes, &tmap_q, p * 128, t * a.H + hg * 128, q_full);
+        tma_load_2d(q_s + p * kMlaQPanelBytes, &tmap_q, p * 32, t * a.H + hg * 128, q_full);   // x in 4-byte units
       bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
       auto issue_qk = [&](int j) -> bool {
         const int b = j & 1, kvb = j % kMlaBufs;
