@@ -228,6 +228,43 @@ def extra_measurements(dev, peaks):
     return out
 
 
+def run_profile_case(args):
+    """Reduced cases of the sparse-MLA and decode kernels, sized for a profiler capture (a few hundred MB
+    on the device, larger than L2): 512 prefill tokens, or a decode step of 8 sequences at 131072 context."""
+    from llmdivedeep_b200 import layer, ops
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(3)
+    fp8 = torch.float8_e4m3fn
+    if args.case == "mla_prefill_small":
+        T, S, H, K = 512, 32768, 128, TOPK
+        q = torch.randn(T, H, 576, device=dev, dtype=torch.bfloat16, generator=g)
+        kv = torch.randn(S, 576, device=dev, dtype=torch.bfloat16, generator=g)
+        idx = (torch.rand(T, K, device=dev, generator=g) * S).int()
+        o = torch.empty(T, H, 512, dtype=torch.bfloat16, device=dev)
+        ms = _time_ms(lambda: ops.sparse_mla_prefill(q, kv, idx, 192 ** -0.5, out=o), iters=max(1, args.steps), warm=args.warmup)
+        info = {"tokens": T, "ms": ms, "tflops_algorithmic": 2.0 * H * 1088 * T * K / ms / 1e9}
+    else:
+        B, CTX = 8, 131072
+        P = CTX // 64
+        n_rows = B * P * 64
+        kcache = torch.randint(0, 120, (n_rows, 128), device=dev, dtype=torch.uint8, generator=g).view(fp8)
+        kscale = torch.rand(n_rows, device=dev, generator=g) * 0.01 + 0.001
+        table = torch.randperm(B * P, device=dev, generator=g).int().view(B, P)
+        ctx = torch.full((B,), CTX, dtype=torch.int32, device=dev)
+        q8 = (torch.randn(B, HEADS, DIM, device=dev, generator=g) * 50).to(fp8)
+        w = torch.randn(B, HEADS, device=dev, generator=g) / 8
+        latent = torch.randint(0, 120, (n_rows, 656), device=dev, dtype=torch.uint8, generator=g)
+        latent[:, 512:528] = torch.full((4,), 0.01, device=dev).view(torch.uint8).repeat(n_rows, 1)
+        latent[:, 528:] = torch.randn(n_rows, 64, device=dev, generator=g).to(torch.bfloat16).view(torch.uint8)
+        qd = torch.randn(B, 128, 576, device=dev, dtype=torch.bfloat16, generator=g)
+        dws = layer.DecodeWorkspace(B, 128, CTX, TOPK, dev)
+        ms = _time_ms(lambda: layer.dsa_decode_step(q8, w, kcache, kscale, table, ctx, qd, latent, 192 ** -0.5, dws),
+                      iters=max(1, args.steps), warm=args.warmup)
+        info = {"batch": B, "context": CTX, "us_per_step": ms * 1e3}
+    ops.check_status(dev)
+    print(json.dumps({"profile_case": args.case, "not_a_bench_value": True, **info}))
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -245,6 +282,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the secondary measurements (sparse MLA prefill, decode step)")
+    ap.add_argument("--case", default="headline", choices=["headline", "mla_prefill_small", "decode_small"],
+                    help="anything but 'headline' runs a few launches of a reduced case for profiler captures and "
+                         "prints a line marked as such, not a bench value")
     ap.add_argument("--rows", type=int, default=T_ROWS,
                     help="query rows per step; anything but 4096 is a reduced case for profiler captures, not a bench value")
     args = ap.parse_args()
@@ -256,6 +296,9 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.case != "headline":
+        run_profile_case(args)
         return
     args.warmup = max(args.warmup, 3)
 
