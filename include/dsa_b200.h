@@ -38,11 +38,22 @@ extern "C" {
 
 #define DSA_W_F32 0
 #define DSA_W_BF16 1
+#define DSA_X_F32 0
+#define DSA_X_BF16 1
 
 /* Library version (major*10000 + minor*100 + patch). */
 int dsa_version(void);
 /* Message of the most recent error on the calling thread ("" if none). */
 const char* dsa_last_error_string(void);
+
+/* Per-block FP8 quantiser, one kernel.  Stands in for fp8_quant_per_block
+ * (sparse_attn/DSA.py:102-132): for every block of block_size (64 or 128)
+ * consecutive values, scale = max(absmax, 1e-6) / 448 (fp32) and
+ * q = round_to_e4m3(x / scale).  x is fp32 (DSA_X_F32) or bf16 (DSA_X_BF16),
+ * n_blocks * block_size values, 16-byte aligned; q_fp8 gets one byte per value,
+ * scale one fp32 per block.  Bytes and scales equal the reference's CPU result. */
+int dsa_fp8_quant_per_block(const void* x, int x_dtype, int64_t n_blocks, int block_size, void* q_fp8, float* scale,
+                            void* stream);
 
 /* Lightning-indexer logits, contiguous keys.
  *   logits[t, s] = k_scale[s] * sum_h w[t,h] * relu(q[t,h,:] . k[s,:])  for ks[t] <= s < ke[t].

@@ -59,17 +59,11 @@ def try_import_deep_gemm():
 
 
 def fp8_quant_per_block(x: torch.Tensor, block_size: int = INDEXER_BLOCK_SIZE) -> Tuple[torch.Tensor, torch.Tensor]:
-    """bf16 -> e4m3 with one fp32 scale per ``block_size`` values of the last dim
+    """bf16/fp32 -> e4m3 with one fp32 scale per ``block_size`` values of the last dim
     (sparse_attn/DSA.py:102-132): scale = max(absmax, 1e-6) / 448; the scale tensor drops its last
-    dim when a row is a single block."""
-    last = x.shape[-1]
-    assert last % block_size == 0, f"last dim {last} not multiple of block {block_size}"
-    nb = last // block_size
-    blocks = x.reshape(-1, nb, block_size).to(torch.float32)
-    scale = blocks.abs().amax(dim=-1, keepdim=True).clamp_min(1e-6) / _FP8_MAX
-    q = (blocks / scale).to(_FP8).view(x.shape)
-    scale = scale.squeeze(-1)
-    return q, (scale.view(x.shape[:-1]) if nb == 1 else scale.view(*x.shape[:-1], nb))
+    dim when a row is a single block.  One fused kernel; its bytes and scales equal the
+    reference's CPU result (both divisions are IEEE round-to-nearest)."""
+    return ops.fp8_quant_per_block(x, block_size)
 
 
 def _fold(w: torch.Tensor, q_scale: torch.Tensor, head_dim: int) -> torch.Tensor:

@@ -57,6 +57,9 @@ int sparse_mla_decode_launch(const void* q, const void* cache, const int32_t* bl
                              cudaStream_t stream);
 size_t mla_decode_workspace_bytes(int B, int H, int K);
 
+int fp8_quant_launch(const void* x, int x_is_bf16, int64_t n_blocks, int block, void* q, float* scale,
+                     cudaStream_t stream);
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace dsa
@@ -167,6 +170,18 @@ int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int
 size_t dsa_sparse_mla_decode_workspace_bytes(int B, int H, int K) {
   if (B <= 0 || H <= 0 || K <= 0) return 0;
   return mla_decode_workspace_bytes(B, H, K);
+}
+
+int dsa_fp8_quant_per_block(const void* x, int x_dtype, int64_t n_blocks, int block_size, void* q_fp8, float* scale,
+                            void* stream) {
+  g_err[0] = 0;
+  if (n_blocks < 0) return set_error(DSA_ERR_SHAPE, "fp8_quant_per_block: negative size");
+  if (n_blocks == 0) return DSA_OK;
+  if (!x || !q_fp8 || !scale) return set_error(DSA_ERR_ARG, "fp8_quant_per_block: NULL pointer argument");
+  if (x_dtype != DSA_X_F32 && x_dtype != DSA_X_BF16) return set_error(DSA_ERR_ARG, "fp8_quant_per_block: bad x_dtype");
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q_fp8) & 3))
+    return set_error(DSA_ERR_ALIGN, "fp8_quant_per_block: x must be 16-byte and q_fp8 4-byte aligned");
+  return fp8_quant_launch(x, x_dtype == DSA_X_BF16, n_blocks, block_size, q_fp8, scale, static_cast<cudaStream_t>(stream));
 }
 
 static const int kMinChunkRows = 256;

@@ -325,3 +325,23 @@ class HostIndexerPipeline:
                 drained[i].record(self.copy_out)
         main.wait_stream(self.copy_out)
         return out_host
+
+
+def fp8_quant_per_block(x: torch.Tensor, block_size: int = 128):
+    """One-kernel FP8 e4m3 quantiser with the reference's semantics (sparse_attn/DSA.py:102-132):
+    returns (q float8_e4m3fn with x's shape, scale fp32); the scale drops its last dim when a row
+    is one block.  x is bf16 or fp32 on a CUDA device."""
+    _need_cuda(x)
+    last = x.shape[-1]
+    assert last % block_size == 0, f"last dim {last} not multiple of block {block_size}"
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        x = x.float()
+    x = x.contiguous()
+    nb = last // block_size
+    n_blocks = x.numel() // block_size
+    q = torch.empty(x.shape, dtype=FP8, device=x.device)
+    scale = torch.empty(n_blocks, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    check(lib.dsa_fp8_quant_per_block(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, n_blocks, block_size,
+                                      _ptr(q), _ptr(scale), _stream()))
+    return q, (scale.view(x.shape[:-1]) if nb == 1 else scale.view(*x.shape[:-1], nb))
