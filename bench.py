@@ -177,6 +177,26 @@ def extra_measurements(dev, peaks):
     fp8 = torch.float8_e4m3fn
     out = {}
     g = torch.Generator(device=dev).manual_seed(7)
+    # ---- the reference's own indexer table: square causal, logits + top-k, ms ------------------
+    published = {8192: 1.71, 16384: 5.49, 32768: 19.97}     # sparse_attn/README.md:259-261 (deep_gemm + torch.topk, 1x B200)
+    rows = []
+    for S in (8192, 16384, 32768):
+        q8 = (torch.randn(S, HEADS, DIM, device=dev, generator=g) * 60).to(torch.float8_e4m3fn)
+        k8 = (torch.randn(S, DIM, device=dev, generator=g) * 60).to(torch.float8_e4m3fn)
+        ksc = torch.rand(S, device=dev, generator=g) * 0.01 + 0.001
+        w = torch.randn(S, HEADS, device=dev, generator=g) * 0.01
+        ks = torch.zeros(S, dtype=torch.int32, device=dev)
+        ke = torch.arange(1, S + 1, dtype=torch.int32, device=dev)
+        wsq = torch.empty(ops._lib.load().dsa_indexer_topk_workspace_bytes(S, S), dtype=torch.uint8, device=dev)
+        oi = torch.empty(S, min(TOPK, S), dtype=torch.int32, device=dev)
+        ms = _time_ms(lambda: ops.indexer_topk(q8, k8, ksc, w, ks, ke, TOPK, workspace=wsq, out=oi), iters=5)
+        rows.append({"seq_len": S, "ms": ms, "reference_published_ms": published[S], "speedup": published[S] / ms})
+        del q8, k8, ksc, w, wsq, oi
+    torch.cuda.empty_cache()
+    out["indexer_logits_topk_square_causal"] = {
+        "what": "IndexerSimulator.logits_step shape: S queries x S keys, causal, 64 heads x 128, k=2048; the reference's "
+                "published numbers are deep_gemm.fp8_mqa_logits + torch.topk on one B200 (its README table)",
+        "rows": rows}
     # ---- sparse MLA prefill ---------------------------------------------------------
     T = S = 32768
     H, K = 128, TOPK
