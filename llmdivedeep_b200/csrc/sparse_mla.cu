@@ -36,11 +36,13 @@ constexpr int kMlaDv = 512;
 constexpr int kMlaDvHalf = 256;
 #ifndef DSA_MLA_BLK
 #define DSA_MLA_BLK 64
-#define DSA_MLA_BUFS 1
+#define DSA_MLA_BUFS 2
 #endif
 constexpr int kMlaBlk = DSA_MLA_BLK;              // keys per block
-constexpr int kMlaBufs = DSA_MLA_BUFS;            // KV buffers in shared memory (Q leaves room for 73.7 KB)
+constexpr int kMlaBufs = DSA_MLA_BUFS;            // KV buffers in shared memory
 constexpr int kMlaPanels = kMlaDqk / 64;          // 9 panels of 64 dims (128 bytes)
+constexpr int kMlaQTmemPanels = 5;                // Q panels kept in tensor memory as the A operand
+constexpr int kMlaQSmemPanels = kMlaPanels - kMlaQTmemPanels;   // the remaining 4 stay in shared memory
 constexpr int kMlaQPanelBytes = 128 * 128;        // 128 heads x 128 B
 constexpr int kMlaKPanelBytes = kMlaBlk * 128;    // 32 keys x 128 B
 constexpr int kMlaQBytes = kMlaPanels * kMlaQPanelBytes;   // 147456
@@ -48,11 +50,14 @@ constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;   // 36864 per buffer
 constexpr int kMlaThreads = 288;
 constexpr int kMlaGatherThreads = 128;
 constexpr int kMlaMaxK = 2048;                    // selected slots per query (row ids staged in shared memory)
-constexpr int kMlaSmemBytes = 1024 + kMlaQBytes + kMlaBufs * kMlaKBytes + 1024 + kMlaMaxK * 4;
+constexpr int kMlaQSmemBytes = kMlaQSmemPanels * kMlaQPanelBytes;   // 65536
+constexpr int kMlaSmemBytes = 1024 + kMlaQSmemBytes + kMlaBufs * kMlaKBytes + 1024 + kMlaMaxK * 4;
+static_assert(kMlaBufs * kMlaKBytes >= kMlaQTmemPanels * kMlaQPanelBytes, "the KV buffers double as the staging area of the TMEM-bound Q panels");
 constexpr int kLatentTokenBytes = 656;            // 512 e4m3 + 4 fp32 scales + 64 bf16 rope
 constexpr int kLatentPage = 64;
 // tensor-memory columns
-constexpr uint32_t kColO = 0, kColS = 256, kColP = kColS + 2 * kMlaBlk, kMlaTmemCols = 512;   // S: 2 x Blk, P: 2 x Blk/2 columns
+constexpr uint32_t kColO = 0, kColS = 256, kColP = kColS + kMlaBlk, kColQ = kColP + kMlaBlk / 2, kMlaTmemCols = 512;
+static_assert(kColQ + kMlaQTmemPanels * 32 <= kMlaTmemCols, "tensor memory budget: O 256, S Blk, P Blk/2, Q 32 per panel");
 
 struct MlaArgs {
   const __nv_bfloat16* kv;        // prefill: [S_kv, 576] bf16
@@ -174,8 +179,8 @@ __global__ void __launch_bounds__(kMlaThreads, 1)
 sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_s = smem;                               // 9 panels [128 heads x 128 B]
-  uint8_t* kv_s = q_s + kMlaQBytes;                  // 2 buffers x 9 panels [32 keys x 128 B]
+  uint8_t* q_s = smem;                               // Q panels 5..8 [128 heads x 128 B]
+  uint8_t* kv_s = q_s + kMlaQSmemBytes;              // KV buffers x 9 panels [Blk keys x 128 B]; first: staging of Q panels 0..4
   uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kMlaBufs * kMlaKBytes);
   uint64_t* q_full = bars + 0;
   uint64_t* o_final = bars + 1;
@@ -183,8 +188,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
   uint64_t* kv_free = bars + 4;                      // [2] P.V of the block finished: its KV buffer is free
   uint64_t* s_full = bars + 6;                       // [2] MMA -> softmax
   uint64_t* p_full = bars + 8;                       // [2] softmax -> MMA
-  uint64_t* pv_done = bars + 10;                     // [2] P.V of block j finished: O is quiescent
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* pv_done = bars + 10;                     // [2] P.V of block j finished: O is quiescent, P is free
+  uint64_t* s_free = bars + 12;                      // softmax has read S into registers
+  uint64_t* q_moved = bars + 13;                     // Q panels 0..4 are in tensor memory, the staging area is free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_s = const_cast<int*>(abort_flag) + 1;
   int* rows_all = reinterpret_cast<int*>(kv_s + kMlaBufs * kMlaKBytes + 1024);   // [kMlaMaxK] row id per slot, -1 = empty
@@ -206,6 +213,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
       mbar_init(&p_full[b], 128);
       mbar_init(&pv_done[b], 1);
     }
+    mbar_init(s_free, 128);
+    mbar_init(q_moved, 128);
     *abort_flag = 0;
     *last_s = -1;
     mbar_fence_init();
@@ -267,23 +276,31 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
       constexpr uint32_t idesc_qk = umma_idesc(1, 1, 0, 0, 128, kMlaBlk);
       constexpr uint32_t idesc_pv = umma_idesc(1, 1, 0, 1, 128, kMlaDvHalf);
       mbar_expect_tx(q_full, kMlaQBytes);
-      for (int p = 0; p < kMlaPanels; ++p)
-        tma_load_2d(q_s + p * kMlaQPanelBytes, &tmap_q, p * 32, t * a.H + hg * 128, q_full);   // x in 4-byte units
-      bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
+      for (int p = 0; p < kMlaPanels; ++p)          // panels 0..4 into the staging area, 5..8 to their place; x in 4-byte units
+        tma_load_2d(p < kMlaQTmemPanels ? kv_s + p * kMlaQPanelBytes : q_s + (p - kMlaQTmemPanels) * kMlaQPanelBytes,
+                    &tmap_q, p * 32, t * a.H + hg * 128, q_full);
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status) && mbar_wait(q_moved, 0, abort_flag, a.status);
       auto issue_qk = [&](int j) -> bool {
-        const int b = j & 1, kvb = j % kMlaBufs;
+        const int kvb = j % kMlaBufs;
         if (!mbar_wait(&kv_full[kvb], (j / kMlaBufs) & 1, abort_flag, a.status)) return false;
+        if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, a.status)) return false;   // S of block j-1 was read
         tc_fence_after();
         const uint8_t* kb = kv_s + kvb * kMlaKBytes;
 #pragma unroll 1
         for (int p = 0; p < kMlaPanels; ++p) {
-          const uint64_t qd = umma_smem_desc(smem_u32(q_s + p * kMlaQPanelBytes), 16, 1024, kSwz128);
           const uint64_t kd = umma_smem_desc(smem_u32(kb + p * kMlaKPanelBytes), 16, 1024, kSwz128);
+          if (p < kMlaQTmemPanels) {               // A operand from tensor memory: no shared-memory read for Q
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_f16_ss(tmem + kColS + b * kMlaBlk, qd + 2 * ks, kd + 2 * ks, idesc_qk, (p | ks) != 0);
+            for (int ks = 0; ks < 4; ++ks)
+              umma_f16_ts(tmem + kColS, tmem + kColQ + p * 32 + 8 * ks, kd + 2 * ks, idesc_qk, (p | ks) != 0);
+          } else {
+            const uint64_t qd = umma_smem_desc(smem_u32(q_s + (p - kMlaQTmemPanels) * kMlaQPanelBytes), 16, 1024, kSwz128);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_f16_ss(tmem + kColS, qd + 2 * ks, kd + 2 * ks, idesc_qk, 1);
+          }
         }
-        umma_commit(&s_full[b]);
+        umma_commit(s_full);
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -296,17 +313,17 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
           qk_done = true;
         }
         if (!ok) break;
-        ok = mbar_wait(&p_full[b], (j >> 1) & 1, abort_flag, a.status);
+        ok = mbar_wait(p_full, j & 1, abort_flag, a.status);
         if (!ok) break;
         tc_fence_after();
         const uint64_t vdesc = umma_smem_desc(smem_u32(kv_s + kvb * kMlaKBytes + vhalf * 4 * kMlaKPanelBytes),
                                               kMlaKPanelBytes, 1024, kSwz128);
 #pragma unroll
         for (int ks = 0; ks < kMlaBlk / 16; ++ks)     // 16 keys per step: 16 rows x 128 B further into each panel
-          umma_f16_ts(tmem + kColO, tmem + kColP + b * (kMlaBlk / 2) + 8 * ks, vdesc + ks * (2048 >> 4), idesc_pv,
+          umma_f16_ts(tmem + kColO, tmem + kColP + 8 * ks, vdesc + ks * (2048 >> 4), idesc_pv,
                       (j | ks) != 0);
         umma_commit(&kv_free[kvb]);
-        umma_commit(&pv_done[b]);
+        umma_commit(&pv_done[j & 1]);
         if (j == nblk - 1) umma_commit(o_final);
         if (!qk_done) ok = issue_qk(j + 1);
       }
@@ -314,6 +331,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
   } else if (warp >= 5) {
     // --------------------------------- gather ---------------------------------
     const int g = threadIdx.x - 160;
+    mbar_wait(q_moved, 0, abort_flag, a.status);      // the buffers hold Q panels until they are in tensor memory
     for (int j = 0; j < nblk; ++j) {
       const int kvb = j % kMlaBufs;
       mbar_wait(&kv_free[kvb], ((j / kMlaBufs) & 1) ^ 1, abort_flag, a.status);
@@ -326,17 +344,35 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
     const int row = threadIdx.x;                       // 0..127 = TMEM lane
     const uint32_t t_row = tmem + (uint32_t(warp * 32) << 16);
     float m = -CUDART_INF_F, l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < nblk; ++j) {
-      const int b = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, a.status));
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, abort_flag, a.status));
+    if (ok) {
+      // this head's row of Q panels 0..4: swizzled shared memory -> packed bf16 pairs in tensor memory
+#pragma unroll 1
+      for (int p = 0; p < kMlaQTmemPanels; ++p) {
+        uint32_t qv[32];
+        const uint8_t* src = kv_s + p * kMlaQPanelBytes + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 w = *reinterpret_cast<const uint4*>(src + ((c ^ (row & 7)) << 4));
+          qv[4 * c + 0] = w.x; qv[4 * c + 1] = w.y; qv[4 * c + 2] = w.z; qv[4 * c + 3] = w.w;
+        }
+        tmem_st32(t_row + kColQ + p * 32, qv);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(q_moved);
+    }
+    for (int j = 0; j < nblk && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, a.status));
       if (!ok) break;
       tc_fence_after();
       uint32_t sv[kMlaBlk];
 #pragma unroll
       for (int c = 0; c < kMlaBlk; c += 32)
-        tmem_ld32(t_row + kColS + b * kMlaBlk + c, *reinterpret_cast<uint32_t(*)[32]>(sv + c));
+        tmem_ld32(t_row + kColS + c, *reinterpret_cast<uint32_t(*)[32]>(sv + c));
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(s_free);                             // the next block's scores may overwrite S now
       float s[kMlaBlk];
       float bmax = -CUDART_INF_F;
       const int* vrow = rows_all + j * kMlaBlk;
@@ -354,7 +390,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         l *= alpha;
         if (j > 0) {
           // O must be quiescent: P.V of the previous block has to be complete
-          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[b ^ 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
           if (!ok) break;
           tc_fence_after();
 #pragma unroll 1
@@ -378,12 +414,17 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         pk[i >> 1] = pack_bf16x2(p0, p1);
       }
       l += psum;
+      if (j > 0) {                                     // P is single-buffered: P.V of the previous block must be done
+        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
+        if (!ok) break;
+        tc_fence_after();
+      }
 #pragma unroll
       for (int c = 0; c < kMlaBlk / 2; c += 16)
-        tmem_st16(t_row + kColP + b * (kMlaBlk / 2) + c, *reinterpret_cast<uint32_t(*)[16]>(pk + c));
+        tmem_st16(t_row + kColP + c, *reinterpret_cast<uint32_t(*)[16]>(pk + c));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full[b]);
+      mbar_arrive(p_full);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
     if (ok) {
