@@ -52,6 +52,7 @@ constexpr int kMlaGatherThreads = 128;
 constexpr int kMlaMaxK = 2048;                    // selected slots per query (row ids staged in shared memory)
 constexpr int kMlaQSmemBytes = kMlaQSmemPanels * kMlaQPanelBytes;   // 65536
 constexpr int kMlaSmemBytes = 1024 + kMlaQSmemBytes + kMlaBufs * kMlaKBytes + 1024 + kMlaMaxK * 4;
+static_assert(kMlaBufs <= 2, "descriptor selection assumes one or two KV buffers");
 static_assert(kMlaBufs * kMlaKBytes >= kMlaQTmemPanels * kMlaQPanelBytes, "the KV buffers double as the staging area of the TMEM-bound Q panels");
 constexpr int kLatentTokenBytes = 656;            // 512 e4m3 + 4 fp32 scales + 64 bf16 rope
 constexpr int kLatentPage = 64;
@@ -280,24 +281,34 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         tma_load_2d(p < kMlaQTmemPanels ? kv_s + p * kMlaQPanelBytes : q_s + (p - kMlaQTmemPanels) * kMlaQPanelBytes,
                     &tmap_q, p * 32, t * a.H + hg * 128, q_full);
       bool ok = mbar_wait(q_full, 0, abort_flag, a.status) && mbar_wait(q_moved, 0, abort_flag, a.status);
+      // The issuing thread is a single lane: every instruction between two MMAs delays the tensor pipe
+      // (a 64-key MMA takes ~48 cycles), so descriptors are built once and the 36 MMAs of a block are
+      // straight-line code with compile-time offsets.
+      uint64_t qdesc[kMlaQSmemPanels];
+#pragma unroll
+      for (int p = 0; p < kMlaQSmemPanels; ++p)
+        qdesc[p] = umma_smem_desc(smem_u32(q_s + p * kMlaQPanelBytes), 16, 1024, kSwz128);
+      uint64_t kdesc[kMlaBufs], vdesc_b[kMlaBufs];
+#pragma unroll
+      for (int b = 0; b < kMlaBufs; ++b) {
+        kdesc[b] = umma_smem_desc(smem_u32(kv_s + b * kMlaKBytes), 16, 1024, kSwz128);
+        vdesc_b[b] = umma_smem_desc(smem_u32(kv_s + b * kMlaKBytes + vhalf * 4 * kMlaKPanelBytes), kMlaKPanelBytes, 1024, kSwz128);
+      }
       auto issue_qk = [&](int j) -> bool {
         const int kvb = j % kMlaBufs;
         if (!mbar_wait(&kv_full[kvb], (j / kMlaBufs) & 1, abort_flag, a.status)) return false;
         if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, a.status)) return false;   // S of block j-1 was read
         tc_fence_after();
-        const uint8_t* kb = kv_s + kvb * kMlaKBytes;
-#pragma unroll 1
+        const uint64_t kd0 = kMlaBufs == 1 ? kdesc[0] : (kvb ? kdesc[kMlaBufs - 1] : kdesc[0]);
+#pragma unroll
         for (int p = 0; p < kMlaPanels; ++p) {
-          const uint64_t kd = umma_smem_desc(smem_u32(kb + p * kMlaKPanelBytes), 16, 1024, kSwz128);
-          if (p < kMlaQTmemPanels) {               // A operand from tensor memory: no shared-memory read for Q
+          const uint64_t kd = kd0 + uint64_t((p * kMlaKPanelBytes) >> 4);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
+          for (int ks = 0; ks < 4; ++ks) {
+            if (p < kMlaQTmemPanels)                 // A operand from tensor memory: no shared-memory read for Q
               umma_f16_ts(tmem + kColS, tmem + kColQ + p * 32 + 8 * ks, kd + 2 * ks, idesc_qk, (p | ks) != 0);
-          } else {
-            const uint64_t qd = umma_smem_desc(smem_u32(q_s + (p - kMlaQTmemPanels) * kMlaQPanelBytes), 16, 1024, kSwz128);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_f16_ss(tmem + kColS, qd + 2 * ks, kd + 2 * ks, idesc_qk, 1);
+            else
+              umma_f16_ss(tmem + kColS, qdesc[p < kMlaQTmemPanels ? 0 : p - kMlaQTmemPanels] + 2 * ks, kd + 2 * ks, idesc_qk, 1);
           }
         }
         umma_commit(s_full);
@@ -316,8 +327,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         ok = mbar_wait(p_full, j & 1, abort_flag, a.status);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t vdesc = umma_smem_desc(smem_u32(kv_s + kvb * kMlaKBytes + vhalf * 4 * kMlaKPanelBytes),
-                                              kMlaKPanelBytes, 1024, kSwz128);
+        const uint64_t vdesc = kMlaBufs == 1 ? vdesc_b[0] : (kvb ? vdesc_b[kMlaBufs - 1] : vdesc_b[0]);
 #pragma unroll
         for (int ks = 0; ks < kMlaBlk / 16; ++ks)     // 16 keys per step: 16 rows x 128 B further into each panel
           umma_f16_ts(tmem + kColO, tmem + kColP + 8 * ks, vdesc + ks * (2048 >> 4), idesc_pv,
