@@ -59,7 +59,7 @@ struct IdxCfg {
   static constexpr int KSTEPS = D / 32;
   static constexpr int K_TILE_BYTES = kTileKeys * D;
   static constexpr int Q_TILE_BYTES = N * D;
-  static constexpr int STAGES = PAGED ? 10 : ((QB == 1) ? 6 : 4);
+  static constexpr int STAGES = PAGED ? 8 : 4;           // power of two: stage and phase come from shifts in the single-lane loops
   static constexpr int TMEM_COLS = (2 * N < 32) ? 32 : 2 * N;
   static constexpr uint64_t SWZ = (D == 128) ? kSwz128 : kSwz64;
   static constexpr uint32_t SBO = 8 * D;                 // 8 rows of D bytes
@@ -266,9 +266,15 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         // never waits on a dependent global load per tile
         const int n_pages = (min(a.ke[qb], a.S) + kPageTokens - 1) / kPageTokens;
         __syncwarp();
-        for (int i = lane; i < 2 * (t_hi - t_lo); i += 32) {
+        for (int i = lane; i < 2 * (t_hi - t_lo); i += 32) {   // store the first cache row of each page, -1 = none
           const int page = 2 * t_lo + i;
-          my_pages[i] = page < n_pages ? __ldg(a.block_table + (int64_t)qb * a.table_stride + page) : -2;
+          int r = -1;
+          if (page < n_pages) {
+            const int phys = __ldg(a.block_table + (int64_t)qb * a.table_stride + page);
+            if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows) r = phys * kPageTokens;
+            else if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+          }
+          my_pages[i] = r;
         }
         __syncwarp();
       }
@@ -296,21 +302,9 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             tma_load_2d(dst, &tmap_k, 0, kt * kTileKeys, &k_full[st]);
           } else {
             // two 64-token pages per tile; a missing or out-of-range page is skipped
-            int rows[2];
-            uint32_t bytes = 0;
-#pragma unroll
-            for (int p = 0; p < 2; ++p) {
-              rows[p] = -1;
-              const int phys = my_pages[2 * (kt - t_lo) + p];    // -2: beyond the sequence's last page
-              if (phys != -2) {
-                if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows) {
-                  rows[p] = phys * kPageTokens;
-                  bytes += C::K_TILE_BYTES / 2;
-                } else if (a.status) {
-                  atomicCAS(a.status, kStatusOk, kStatusBadIndex);
-                }
-              }
-            }
+            const int2 rows2 = *reinterpret_cast<const int2*>(my_pages + 2 * (kt - t_lo));   // validated above
+            const int rows[2] = {rows2.x, rows2.y};
+            const uint32_t bytes = ((rows2.x >= 0) + (rows2.y >= 0)) * (C::K_TILE_BYTES / 2);
             if (bytes) {
               mbar_expect_tx(&k_full[st], bytes);
 #pragma unroll
