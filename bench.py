@@ -37,6 +37,7 @@ import torch
 
 T_ROWS, S_KEYS, HEADS, DIM, TOPK = 4096, 65536, 64, 128, 2048
 N_INPUT_SETS = 4
+E2E_CHUNKS = 4
 METRIC = "DSA prefill tokens/s (lightning indexer + top-k, 4096 query rows x 65536 keys, k=2048)"
 WORKLOAD = "standalone indexer+top-k: 4096 query rows (pos 61440-65535) x 65536 keys, 64 heads x 128, fp8 e4m3, k=2048"
 
@@ -368,7 +369,7 @@ def main():
     host_out = torch.empty(T_ROWS, TOPK, dtype=torch.int32).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
     d2h = host_out.numel() * 4
-    pipe = ops.HostIndexerPipeline(T_ROWS, S_KEYS, HEADS, DIM, TOPK, dev, chunks=4, w_dtype=torch.bfloat16)
+    pipe = ops.HostIndexerPipeline(T_ROWS, S_KEYS, HEADS, DIM, TOPK, dev, chunks=E2E_CHUNKS, w_dtype=torch.bfloat16)
 
     def e2e_step(i):
         q8h, k8h, ksch, wh, ksh, keh = host_sets[i % 2]
@@ -434,7 +435,7 @@ def main():
                    "sharding": "query rows per rank, keys replicated, no collective"},
         "e2e": {"value": world * T_ROWS * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
-                "how": "ops.HostIndexerPipeline: pinned host tensors in and out, 4 row chunks, copies on side streams"},
+                "how": f"ops.HostIndexerPipeline: pinned host tensors in and out, {E2E_CHUNKS} row chunks, copies on side streams"},
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "indexer_logits_kernel<64,128,4>", "achieved": achieved,
