@@ -286,6 +286,41 @@ def run_profile_case(args):
     print(json.dumps({"profile_case": args.case, "not_a_bench_value": True, **info}))
 
 
+def sharded_mla_measurement(dev, rank, world):
+    """Sparse MLA prefill of ONE sequence split over the ranks (strong scaling), output all-gathered over
+    NCCL: by query rows (the scaling path) and by heads (128/world heads per rank, every rank gathers all rows).
+    8192 tokens x 128 heads x 2048 selected keys of a 32768-row latent KV; max over ranks of CUDA-event times."""
+    import torch.distributed as dist
+    from llmdivedeep_b200 import ops, sharding as sh
+    T, S, H, K = 8192, 32768, 128, TOPK
+    g = torch.Generator(device=dev).manual_seed(11)               # same tensors on every rank
+    q = torch.randn(T, H, 576, device=dev, dtype=torch.bfloat16, generator=g)
+    kv = torch.randn(S, 576, device=dev, dtype=torch.bfloat16, generator=g)
+    idx = (torch.rand(T, K, device=dev, generator=g) * S).int()
+    rows = sh.rows_of(sh.row_chunks(T, world, rank, 256), device=dev)
+    q_rows, idx_rows = q[rows].contiguous(), idx[rows].contiguous()
+    h0, h1 = sh.head_range(H, world, rank)
+    q_heads = q[:, h0:h1].contiguous()
+
+    def by_rows():
+        return sh.all_gather_rows(ops.sparse_mla_prefill(q_rows, kv, idx_rows, 192 ** -0.5), T, world, 256)
+
+    def by_heads():
+        return sh.all_gather_heads(ops.sparse_mla_prefill(q_heads, kv, idx, 192 ** -0.5), H, world)
+
+    res = {}
+    for name, fn in (("rows", by_rows), ("heads", by_heads)):
+        ms = torch.tensor([_time_ms(fn, iters=3, warm=1)], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        res[name + "_ms"] = float(ms.item())
+    one = _time_ms(lambda: ops.sparse_mla_prefill(q, kv, idx, 192 ** -0.5), iters=2, warm=1) if rank == 0 else 0.0
+    same = bool(torch.equal(by_rows(), by_heads()))
+    res.update({"single_gpu_ms": one, "n_gpus": world, "rows_equals_heads_result": same,
+                "workload": "8192 tokens x 128 heads x 2048 selected keys, bf16, one sequence split over the ranks; "
+                            "times include the NCCL all-gather of the output"})
+    return res
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -328,6 +363,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's version banner must not share stdout with the JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -411,6 +447,9 @@ def main():
     torch.cuda.synchronize()
     topk_ms = e0.elapsed_time(e1) / args.steps
 
+    sharded = None
+    if world > 1 and not args.no_extra and args.rows == 4096:
+        sharded = sharded_mla_measurement(dev, rank, world)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -450,6 +489,8 @@ def main():
         del sets, host_sets, pipe, ws, logits
         torch.cuda.empty_cache()
         line["extra"] = extra_measurements(dev, peaks)
+    if sharded is not None:
+        line.setdefault("extra", {})["sparse_mla_prefill_sharded"] = sharded
     if not args.no_cpu_baseline:
         rows = 512
         cpu_port_rows_per_s(16)

@@ -57,38 +57,73 @@ def batch_range(batch: int, world: int, rank: int) -> Tuple[int, int]:
     return head_range(batch, world, rank)
 
 
+_PERM_CACHE = {}
+
+
+def _all_gather_flat(gathered: torch.Tensor, buf: torch.Tensor, world: int, group=None) -> None:
+    """gathered[r * n : (r + 1) * n] = rank r's buf (n = buf.shape[0]); one fused collective under nccl,
+    the list form elsewhere (gloo on CPU)."""
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(gathered, buf, group=group)
+    else:
+        dist.all_gather(list(gathered.view((world,) + tuple(buf.shape)).unbind(0)), buf, group=group)
+
+
+def _row_permutation(n_rows: int, world: int, chunk: int, pad: int, device) -> torch.Tensor:
+    """For every output row, its position in the rank-major gathered buffer [world * pad]."""
+    key = (n_rows, world, chunk, pad, str(device))
+    if key not in _PERM_CACHE:
+        perm = torch.empty(n_rows, dtype=torch.long)
+        for r in range(world):
+            rows = rows_of(row_chunks(n_rows, world, r, chunk))
+            perm[rows] = r * pad + torch.arange(rows.numel())
+        _PERM_CACHE[key] = perm.to(device)
+    return _PERM_CACHE[key]
+
+
 def all_gather_rows(local: torch.Tensor, n_rows: int, world: int, chunk: int = 256, group=None) -> torch.Tensor:
-    """Assemble the full [n_rows, ...] output from per-rank row-chunk results (row sharding).
-    Ranks may hold different row counts; results are padded to the largest for the collective."""
+    """Assemble the full [n_rows, ...] output from per-rank row-chunk results (row sharding): one
+    all-gather into a rank-major buffer (ranks padded to the largest row count) and one gather that
+    puts the rows back in order."""
     counts = [sum(b - a for a, b in row_chunks(n_rows, world, r, chunk)) for r in range(world)]
     pad = max(counts)
-    buf = local.new_zeros((pad,) + tuple(local.shape[1:]))
-    buf[: local.shape[0]] = local
-    parts = [torch.empty_like(buf) for _ in range(world)]
-    dist.all_gather(parts, buf, group=group)
-    out = local.new_empty((n_rows,) + tuple(local.shape[1:]))
-    for r in range(world):
-        out[rows_of(row_chunks(n_rows, world, r, chunk), device=local.device)] = parts[r][: counts[r]]
-    return out
+    if local.shape[0] == pad:
+        buf = local.contiguous()
+    else:
+        buf = local.new_zeros((pad,) + tuple(local.shape[1:]))
+        buf[: local.shape[0]] = local
+    gathered = local.new_empty((world * pad,) + tuple(local.shape[1:]))
+    _all_gather_flat(gathered, buf, world, group)
+    return gathered.index_select(0, _row_permutation(n_rows, world, chunk, pad, local.device))
 
 
 def all_gather_heads(local: torch.Tensor, n_heads: int, world: int, group=None) -> torch.Tensor:
     """Assemble [T, n_heads, D] from per-rank head slices [T, h_r, D] (head sharding)."""
     sizes = [head_range(n_heads, world, r) for r in range(world)]
     pad = max(b - a for a, b in sizes)
-    buf = local.new_zeros((local.shape[0], pad, local.shape[2]))
-    buf[:, : local.shape[1]] = local
-    parts = [torch.empty_like(buf) for _ in range(world)]
-    dist.all_gather(parts, buf.contiguous(), group=group)
-    return torch.cat([parts[r][:, : b - a] for r, (a, b) in enumerate(sizes)], dim=1)
+    if local.shape[1] == pad:
+        buf = local.contiguous()
+    else:
+        buf = local.new_zeros((local.shape[0], pad, local.shape[2]))
+        buf[:, : local.shape[1]] = local
+    gathered = local.new_empty((world,) + tuple(buf.shape))
+    _all_gather_flat(gathered.view((world * buf.shape[0],) + tuple(buf.shape[1:])), buf, world, group)
+    if all(b - a == pad for a, b in sizes):
+        return gathered.permute(1, 0, 2, 3).reshape(local.shape[0], n_heads, local.shape[2])
+    return torch.cat([gathered[r][:, : b - a] for r, (a, b) in enumerate(sizes)], dim=1)
 
 
 def all_gather_batch(local: torch.Tensor, batch: int, world: int, group=None) -> torch.Tensor:
     """Assemble [batch, ...] decode outputs from contiguous per-rank slices."""
     sizes = [batch_range(batch, world, r) for r in range(world)]
     pad = max(b - a for a, b in sizes)
-    buf = local.new_zeros((pad,) + tuple(local.shape[1:]))
-    buf[: local.shape[0]] = local
-    parts = [torch.empty_like(buf) for _ in range(world)]
-    dist.all_gather(parts, buf, group=group)
-    return torch.cat([parts[r][: b - a] for r, (a, b) in enumerate(sizes)], dim=0)
+    if local.shape[0] == pad:
+        buf = local.contiguous()
+    else:
+        buf = local.new_zeros((pad,) + tuple(local.shape[1:]))
+        buf[: local.shape[0]] = local
+    gathered = local.new_empty((world, pad) + tuple(local.shape[1:]))
+    _all_gather_flat(gathered.view((world * pad,) + tuple(local.shape[1:])), buf, world, group)
+    if all(b - a == pad for a, b in sizes):
+        return gathered.reshape((batch,) + tuple(local.shape[1:]))
+    return torch.cat([gathered[r][: b - a] for r, (a, b) in enumerate(sizes)], dim=0)
