@@ -113,3 +113,64 @@ def test_full_size_row_property():
     lo_sel = torch.where(sel, x, torch.full_like(x, float("inf"))).amin(1)
     hi_uns = torch.where(sel, torch.full_like(x, float("-inf")), x).amax(1)
     assert bool((lo_sel >= hi_uns).all())
+
+
+def _two_pass(x, k, ks=None, ke=None):
+    """The same call with the sampled single pass switched off (every row takes the two-pass path)."""
+    import os
+    os.environ["DSA_TOPK_NO_SAMPLE"] = "1"
+    try:
+        return ops.topk_select(x, k, ks, ke)
+    finally:
+        os.environ.pop("DSA_TOPK_NO_SAMPLE", None)
+
+
+def _adversarial_rows(S, g):
+    """Rows built to mislead a sample taken as one 128-column block in every 16: a ramp, the large
+    values packed into few blocks, a two-level row with more ties than the candidate capacity, a
+    near-constant row, and a row whose large values sit exactly in the sampled blocks."""
+    rows = [torch.randn(S, device=DEV, generator=g),
+            torch.arange(S, device=DEV, dtype=torch.float32),
+            -torch.arange(S, device=DEV, dtype=torch.float32)]
+    r = torch.randn(S, device=DEV, generator=g)
+    r[4096:4096 + 3000] += 100.0                              # contiguous spike wider than k
+    rows.append(r)
+    r = torch.zeros(S, device=DEV)
+    r[torch.randperm(S, device=DEV, generator=g)[:6000]] = 1.0   # 6000 tied maxima
+    rows.append(r)
+    rows.append(torch.full((S,), 3.0, device=DEV) + 1e-7 * torch.randn(S, device=DEV, generator=g))
+    r = torch.randn(S, device=DEV, generator=g)
+    blk = torch.arange(S, device=DEV) // 128
+    r[(blk % 16) == 8] += 6.0                                 # only the sampled blocks are large
+    rows.append(r)
+    r = torch.randn(S, device=DEV, generator=g)
+    r[(blk % 16) == 8] -= 6.0                                 # the sampled blocks are small
+    rows.append(r)
+    return torch.stack(rows)
+
+
+@pytest.mark.parametrize("S,k", [(65536, 2048), (131072, 2048), (16384, 2048), (40000, 512), (300000, 2048)])
+def test_sampled_pass_equals_two_pass_on_adversarial_rows(S, k):
+    g = torch.Generator(device=DEV).manual_seed(S + k)
+    x = _adversarial_rows(S, g)
+    a = ops.topk_select(x, k)
+    b = _two_pass(x, k)
+    assert torch.equal(a.sort(dim=1).values, b.sort(dim=1).values)
+    _sets_equal_with_ties(x, a, k)
+    T = x.shape[0]
+    ks = torch.randint(0, S // 8, (T,), device=DEV, dtype=torch.int32, generator=g)
+    ke = torch.randint(S - S // 8, S + 1, (T,), device=DEV, dtype=torch.int32, generator=g)
+    a = ops.topk_select(x, k, ks, ke)
+    assert torch.equal(a, ops.topk_select(x, k, ks, ke)), "not deterministic"
+    assert torch.equal(a.sort(dim=1).values, _two_pass(x, k, ks, ke).sort(dim=1).values)
+
+
+def _sets_equal_with_ties(x, idx, k):
+    """Exact rule: everything above the k-th value is selected, the rest are the lowest columns equal to it."""
+    for t in range(x.shape[0]):
+        row = x[t]
+        kth = row.topk(k).values[-1]
+        above = (row > kth).nonzero().flatten()
+        tied = (row == kth).nonzero().flatten()[: k - above.numel()]
+        want = torch.cat([above, tied]).sort().values
+        assert torch.equal(idx[t].long().sort().values, want), f"row {t}"
