@@ -33,7 +33,7 @@
 namespace dsa {
 
 constexpr int kTileKeys = 128;
-constexpr int kChunkTiles = 64;        // key tiles per work unit
+constexpr int kChunkTiles = 64;        // most key tiles per work unit (launches with few units use fewer)
 constexpr int kPageTokens = 64;
 
 struct IndexerArgs {
@@ -49,6 +49,7 @@ struct IndexerArgs {
   int S;                     // keys (paged: max logical positions = pages_per_seq*64)
   int num_phys_rows;         // paged: rows of the cache
   int w_is_bf16;
+  int chunk_tiles;           // key tiles per work unit, <= kChunkTiles (set by the launcher)
   int* status;
 };
 
@@ -112,8 +113,8 @@ __device__ __forceinline__ bool unit_tiles(const IndexerArgs& a, int u, int n_qb
   int lo, hi;
   token_window<PAGED>(a, qb * QB * NQ, nb * NQ, lo, hi);
   if (hi <= lo) return false;
-  t_lo = max(c * kChunkTiles, lo / kTileKeys);
-  t_hi = min((c + 1) * kChunkTiles, (hi + kTileKeys - 1) / kTileKeys);
+  t_lo = max(c * a.chunk_tiles, lo / kTileKeys);
+  t_hi = min((c + 1) * a.chunk_tiles, (hi + kTileKeys - 1) / kTileKeys);
   return t_lo < t_hi;
 }
 
@@ -121,12 +122,6 @@ __device__ __forceinline__ bool unit_tiles(const IndexerArgs& a, int u, int n_qb
 // its TMEM lane.  Weights of chunk c+1 and its TMEM load are both requested before
 // the math of chunk c, in that order: shared-memory loads queue behind a TMEM load
 // issued earlier by the same warp, so the weights must go first to overlap.
-#ifdef DSA_IDX_NOWLDS   // experiment: no shared-memory weight loads
-#define DSA_WLOAD(p) make_float4(kscale, kscale * 0.5f, kscale * 0.25f, kscale * 2.f)
-#else
-#define DSA_WLOAD(p) (*reinterpret_cast<const float4*>(p))
-#endif
-
 template <int H, int NQ, int CH, int COL0, int NCOLS>
 __device__ __forceinline__ void drain_columns(uint32_t t_lane, const float* __restrict__ w_s,
                                               const int2* __restrict__ win_s, float kscale, int s, bool s_ok,
@@ -136,7 +131,7 @@ __device__ __forceinline__ void drain_columns(uint32_t t_lane, const float* __re
   float4 wv[2][CH / 4];
   uint64_t chain[NCH];
 #pragma unroll
-  for (int i = 0; i < CH / 4; ++i) wv[0][i] = DSA_WLOAD(w_s + COL0 + 4 * i);
+  for (int i = 0; i < CH / 4; ++i) wv[0][i] = *reinterpret_cast<const float4*>(w_s + COL0 + 4 * i);
   tmem_ld16(t_lane + COL0, v[0]);
 #pragma unroll
   for (int c = 0; c < NCOLS; c += CH) {
@@ -145,7 +140,7 @@ __device__ __forceinline__ void drain_columns(uint32_t t_lane, const float* __re
     if (c + CH < NCOLS) {
 #pragma unroll
       for (int i = 0; i < CH / 4; ++i)
-        wv[cur ^ 1][i] = DSA_WLOAD(w_s + COL0 + c + CH + 4 * i);
+        wv[cur ^ 1][i] = *reinterpret_cast<const float4*>(w_s + COL0 + c + CH + 4 * i);
       tmem_ld16(t_lane + COL0 + c + CH, v[cur ^ 1]);
     }
 #pragma unroll
@@ -179,19 +174,6 @@ __device__ __forceinline__ void drain_columns(uint32_t t_lane, const float* __re
     }
   }
 }
-
-#ifdef DSA_IDX_PROFILE
-__device__ long long g_prof[148 * 16];
-#define PROF_T0() long long _pt = clock64()
-#define PROF_ADD(slot) do { long long _n = clock64(); _acc[slot] += _n - _pt; _pt = _n; } while (0)
-#define PROF_DECL() long long _acc[4] = {0, 0, 0, 0}
-#define PROF_STORE(base) do { if (lane == 0) for (int _i = 0; _i < 4; ++_i) g_prof[blockIdx.x * 16 + (base) + _i] = _acc[_i]; } while (0)
-#else
-#define PROF_T0()
-#define PROF_ADD(slot)
-#define PROF_DECL()
-#define PROF_STORE(base)
-#endif
 
 template <int H, int D, int NQ, bool PAGED, int QB, int EPI>
 __global__ void __launch_bounds__(IdxCfg<H, D, NQ, PAGED, QB, EPI>::THREADS, 1)
@@ -254,8 +236,6 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int pidx = warp == 0 ? 0 : 1;
     int* my_pages = pages_s + pidx * 2 * kChunkTiles;
     uint32_t it = 0, nu = 0;
-    PROF_DECL();
-    PROF_T0();
     for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
       int qb, nb, t_lo, t_hi;
       if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
@@ -292,9 +272,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
           if (int(it % PL) != pidx) continue;
           const int st = it % C::STAGES;
-          PROF_ADD(1);
           ok = mbar_wait(&k_empty[st], ((it / C::STAGES) & 1) ^ 1, abort_flag, a.status);
-          PROF_ADD(0);
           if (!ok) break;
           uint8_t* dst = k_s + st * C::K_TILE_BYTES;
           if constexpr (!PAGED) {
@@ -321,8 +299,6 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       it = __shfl_sync(0xffffffffu, it, 0) ;
       if (!ok) break;
     }
-    PROF_ADD(2);
-    if (pidx == 0) PROF_STORE(12);
     // on abort, give copies already in flight a bounded chance to land
     if (lane == 0 && *abort_flag) {
       for (int st = 0; st < C::STAGES; ++st)
@@ -334,26 +310,20 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     // ------------------------------- MMA issuer -------------------------------
     constexpr uint32_t idesc = umma_idesc(0, 0, 0, 0, kTileKeys, C::N);
     uint32_t it = 0, it2 = 0, nu = 0;
-    PROF_DECL();
-    PROF_T0();
     for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
       int qb, nb, t_lo, t_hi;
       if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
       const int qs = nu & 1;
       bool ok = true;
       if (lane == 0) {
-        PROF_ADD(3);
         ok = mbar_wait(&q_full[qs], (nu >> 1) & 1, abort_flag, a.status);
-        PROF_ADD(0);
         for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
           const int st = it % C::STAGES;
           ok = mbar_wait(&k_full[st], (it / C::STAGES) & 1, abort_flag, a.status);
-          PROF_ADD(1);
           const uint64_t kdesc = umma_smem_desc(smem_u32(k_s + st * C::K_TILE_BYTES), 16, C::SBO, C::SWZ);
           for (int b = 0; b < nb && ok; ++b, ++it2) {
             const int acc = it2 & 1;
             ok = mbar_wait(&acc_empty[acc], ((it2 >> 1) & 1) ^ 1, abort_flag, a.status);
-            PROF_ADD(2);
             if (!ok) break;
             tc_fence_after();
             const uint64_t qdesc =
@@ -373,8 +343,6 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       it2 = __shfl_sync(0xffffffffu, it2, 0);
       if (!ok) break;
     }
-    PROF_ADD(3);
-    PROF_STORE(0);
   } else if (warp == 2) {
     // ------------------- stager: head weights and windows per unit -------------------
     uint32_t nu = 0;
@@ -421,15 +389,11 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const uint32_t t_lane = tmem_base + (uint32_t(wq * 32) << 16) + stage * C::N;
     uint32_t it2 = 0, n_mine = 0, nu = 0;
     bool ok = true;
-    PROF_DECL();
-    PROF_T0();
     for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
       int qb, nb, t_lo, t_hi;
       if (!unit_tiles<NQ, QB, PAGED>(a, u, n_qblocks, n_groups, qb, nb, t_lo, t_hi)) continue;
       const int ub = nu & 1;
-      PROF_ADD(3);
       ok = __all_sync(0xffffffffu, mbar_wait(&w_full[ub], (nu >> 1) & 1, abort_flag, a.status));
-      PROF_ADD(0);
       if (!ok) break;
       auto load_kscale = [&](int tile) -> float {
         const int sk = tile * kTileKeys + row;
@@ -464,9 +428,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           const int2* my_win = win_s + ub * C::NTOK + b * NQ;
           float* grp_base = a.logits + (int64_t)g * NQ * a.ld;   // 32-bit offsets from here: NQ * ld < 2^31
           const int n_tok = min(NQ, a.T - g * NQ);
-          PROF_ADD(3);
           ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[stage], n_mine & 1, abort_flag, a.status));
-          PROF_ADD(1);
           if (!ok) break;
           tc_fence_after();
           if constexpr (C::SPLIT == 1) {
@@ -482,7 +444,6 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[stage]);
-          PROF_ADD(2);
           ++n_mine;
         }
       }
@@ -490,9 +451,6 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (lane == 0) mbar_arrive(&w_empty[ub]);
       ++nu;
     }
-    PROF_ADD(3);
-    if (ew == 0) PROF_STORE(4);
-    if (ew == 4) PROF_STORE(8);
   }
 
   tc_fence_before();
@@ -524,12 +482,6 @@ __global__ void fill_masked_kernel(const IndexerArgs a) {
   for (int s = threadIdx.x; s < s_lo; s += blockDim.x) row[s] = -CUDART_INF_F;
   for (int s = s_hi + threadIdx.x; s < a.S; s += blockDim.x) row[s] = -CUDART_INF_F;
 }
-
-#ifdef DSA_IDX_PROFILE
-extern "C" int dsa_debug_read_profile(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_prof, sizeof(long long) * 148 * 16);
-}
-#endif
 
 // ------------------------------- host side ----------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -574,9 +526,10 @@ int make_tmap_2d_u8(CUtensorMap* m, const void* base, uint64_t rows, uint32_t ro
 }
 
 template <int H, int D, int NQ, bool PAGED, int QB, int EPI>
-static int launch_indexer(const void* q, const void* k, const IndexerArgs& a, int clean, cudaStream_t stream) {
+static int launch_indexer(const void* q, const void* k, const IndexerArgs& args, int clean, cudaStream_t stream) {
   using C = IdxCfg<H, D, NQ, PAGED, QB, EPI>;
-  if (a.T == 0 || a.S == 0) return DSA_OK;
+  if (args.T == 0 || args.S == 0) return DSA_OK;
+  IndexerArgs a = args;
   CUtensorMap tq, tk;
   int rc = make_tmap_2d_u8(&tq, q, (uint64_t)a.T * H, D, D, C::N);
   if (rc) return rc;
@@ -586,7 +539,13 @@ static int launch_indexer(const void* q, const void* k, const IndexerArgs& a, in
   const int n_groups = (a.T + NQ - 1) / NQ;
   const int n_qblocks = (n_groups + QB - 1) / QB;
   const int n_tiles = (a.S + kTileKeys - 1) / kTileKeys;
-  const int n_chunks = (n_tiles + kChunkTiles - 1) / kChunkTiles;
+  // Units are dealt to the CTAs round-robin: keep at least six rounds of them so that the last, partly
+  // filled round costs little, by cutting the key range finer when there are few query blocks.
+  a.chunk_tiles = kChunkTiles;
+  while (a.chunk_tiles > 8 &&
+         (int64_t)n_qblocks * ((n_tiles + a.chunk_tiles - 1) / a.chunk_tiles) < 6LL * sm_count())
+    a.chunk_tiles /= 2;
+  const int n_chunks = (n_tiles + a.chunk_tiles - 1) / a.chunk_tiles;
   const int64_t n_units64 = (int64_t)n_qblocks * n_chunks;
   if (n_units64 > 0x7fffffff) return set_error(DSA_ERR_SHAPE, "indexer: too many work units");
   const int n_units = (int)n_units64;

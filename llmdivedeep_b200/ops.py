@@ -262,12 +262,15 @@ class HostIndexerPipeline:
 
     def __init__(self, T: int, S: int, H: int, D: int, k: int, device, chunks: int = 4, w_dtype=torch.float32):
         self.T, self.S, self.H, self.D, self.k, self.device = T, S, H, D, min(k, S), torch.device(device)
-        rows = -(-T // chunks)
-        rows = max(256, -(-rows // 256) * 256)                # whole 256-row groups per chunk
-        self.bounds = [(a, min(T, a + rows)) for a in range(0, T, rows)]
+        self.bounds = self.chunk_bounds(T, chunks)
+        rows = max(b - a for a, b in self.bounds)
         dev = self.device
-        self.k_fp8 = torch.empty(S, D, dtype=FP8, device=dev)
-        self.k_scale = torch.empty(S, dtype=torch.float32, device=dev)
+        self.k_fp8 = [torch.empty(S, D, dtype=FP8, device=dev) for _ in range(2)]       # alternate between calls
+        self.k_scale = [torch.empty(S, dtype=torch.float32, device=dev) for _ in range(2)]
+        self._calls = 0
+        self._k_busy = [None, None]        # per key buffer: event after the last kernels that read it
+        self._slot_busy = [None, None]     # per input staging slot: event after the kernels that read it
+        self._out_busy = [None, None]      # per output slot: event after its device -> host copy
         self.q = [torch.empty(rows, H, D, dtype=FP8, device=dev) for _ in range(2)]
         self.w = [torch.empty(rows, H, dtype=w_dtype, device=dev) for _ in range(2)]
         self.ks = [torch.empty(rows, dtype=torch.int32, device=dev) for _ in range(2)]
@@ -278,25 +281,55 @@ class HostIndexerPipeline:
         self.copy_in = torch.cuda.Stream(device=dev)
         self.copy_out = torch.cuda.Stream(device=dev)
 
-    def __call__(self, q_host, k_host, k_scale_host, w_host, ks_host, ke_host, out_host) -> torch.Tensor:
-        """All arguments are host tensors (pinned for real overlap); out_host int32 [T, k]."""
+    @staticmethod
+    def chunk_bounds(T: int, chunks: int):
+        """Row ranges of the chunks, in whole 256-row groups.  With four or more chunks the first one is
+        small (its host -> device copy, together with the keys', is the part no kernel can hide) and so is
+        the last (its device -> host copy is exposed the same way); the rows between are split evenly."""
+        groups = -(-T // 256)
+        if chunks < 4 or groups < 2 * chunks:
+            per = max(1, -(-groups // max(chunks, 1)))
+            sizes = [per] * (-(-groups // per))
+        else:
+            first = max(1, groups // 16)
+            last = 2 * first
+            mid = groups - first - last
+            per, extra = divmod(mid, chunks - 2)
+            sizes = [first] + [per + (1 if i >= chunks - 2 - extra else 0) for i in range(chunks - 2)] + [last]
+        bounds, a = [], 0
+        for g in sizes:
+            b = min(T, a + g * 256)
+            if b > a:
+                bounds.append((a, b))
+            a = b
+        return bounds
+
+    def submit(self, q_host, k_host, k_scale_host, w_host, ks_host, ke_host, out_host) -> "torch.cuda.Event":
+        """Enqueue one call; all arguments are host tensors (pinned for real overlap), out_host int32 [T, k].
+        Returns the event after which out_host holds the result.  Nothing here waits on the host, and the
+        current stream is not made to wait for the output copy, so a caller that submits call after call
+        gets the next call's input copies under this call's kernels (staging slots and the two key buffers
+        are handed over by events)."""
         main = torch.cuda.current_stream(self.device)
         n = len(self.bounds)
         in_ready = [torch.cuda.Event() for _ in range(n)]
-        computed = [torch.cuda.Event() for _ in range(n)]
-        drained = [torch.cuda.Event() for _ in range(n)]
-        self.copy_in.wait_stream(main)
-        self.copy_out.wait_stream(main)
+        kb = self._calls & 1
+        if self._calls == 0:                       # staging buffers were allocated on the current stream
+            self.copy_in.wait_stream(main)
+            self.copy_out.wait_stream(main)
+        k_fp8, k_scale = self.k_fp8[kb], self.k_scale[kb]
 
         def stage(i):          # enqueue the host -> device copies of chunk i (events it waits on are already recorded)
             a, b = self.bounds[i]
             s = i & 1
             with torch.cuda.stream(self.copy_in):
                 if i == 0:
-                    self.k_fp8.copy_(k_host, non_blocking=True)
-                    self.k_scale.copy_(k_scale_host, non_blocking=True)
-                if i >= 2:
-                    self.copy_in.wait_event(computed[i - 2])     # staging slot free again
+                    if self._k_busy[kb] is not None:
+                        self.copy_in.wait_event(self._k_busy[kb])    # last kernels that read this key buffer
+                    k_fp8.copy_(k_host, non_blocking=True)
+                    k_scale.copy_(k_scale_host, non_blocking=True)
+                if self._slot_busy[s] is not None:
+                    self.copy_in.wait_event(self._slot_busy[s])      # staging slot free again
                 self.q[s][: b - a].copy_(q_host[a:b], non_blocking=True)
                 self.w[s][: b - a].copy_(w_host[a:b], non_blocking=True)
                 self.ke[s][: b - a].copy_(ke_host[a:b], non_blocking=True)
@@ -309,21 +342,36 @@ class HostIndexerPipeline:
         stage(0)
         if n > 1:
             stage(1)
+        computed = None
         for i, (a, b) in enumerate(self.bounds):
             s = i & 1
             main.wait_event(in_ready[i])
-            if i >= 2:
-                main.wait_event(drained[i - 2])                  # output slot copied out
-            indexer_topk(self.q[s][: b - a], self.k_fp8, self.k_scale, self.w[s][: b - a], self.ks[s][: b - a],
+            if self._out_busy[s] is not None:
+                main.wait_event(self._out_busy[s])                   # output slot copied out
+            indexer_topk(self.q[s][: b - a], k_fp8, k_scale, self.w[s][: b - a], self.ks[s][: b - a],
                          self.ke[s][: b - a], self.k, workspace=self.ws, out=self.out[s][: b - a])
-            computed[i].record(main)
+            computed = torch.cuda.Event()
+            computed.record(main)
+            self._slot_busy[s] = computed
             if i + 2 < n:
                 stage(i + 2)
             with torch.cuda.stream(self.copy_out):
-                self.copy_out.wait_event(computed[i])
+                self.copy_out.wait_event(computed)
                 out_host[a:b].copy_(self.out[s][: b - a], non_blocking=True)
-                drained[i].record(self.copy_out)
-        main.wait_stream(self.copy_out)
+                drained = torch.cuda.Event()
+                drained.record(self.copy_out)
+                self._out_busy[s] = drained
+        self._k_busy[kb] = computed
+        self._calls += 1
+        done = torch.cuda.Event()
+        done.record(self.copy_out)
+        return done
+
+    def __call__(self, q_host, k_host, k_scale_host, w_host, ks_host, ke_host, out_host) -> torch.Tensor:
+        """submit(), then the current stream waits for the output copy: work queued after this call (or a
+        synchronize of the current stream) sees out_host filled."""
+        done = self.submit(q_host, k_host, k_scale_host, w_host, ks_host, ke_host, out_host)
+        torch.cuda.current_stream(self.device).wait_event(done)
         return out_host
 
 

@@ -161,3 +161,20 @@ def test_host_pipeline_matches_device_call():
         torch.cuda.synchronize()
         assert torch.equal(out, want)
     ops.check_status("cuda")
+
+
+def test_host_pipeline_submits_back_to_back():
+    """Several submits in a row with different inputs and separate outputs, no waiting in between: the
+    staging slots and the two key buffers are handed from call to call by events alone."""
+    T, S, K = 2600, 8192, 512
+    pipe = ops.HostIndexerPipeline(T, S, 64, 128, K, "cuda", chunks=5)
+    assert len(pipe.bounds) == 5 and pipe.bounds[0][1] - pipe.bounds[0][0] < pipe.bounds[2][1] - pipe.bounds[2][0]
+    cases = [indexer_inputs(T, S, 64, 128, seed=40 + i, window="random") for i in range(4)]
+    want = [ops.indexer_topk(*to_dev(*c), K).cpu() for c in cases]
+    hosts = [[t.pin_memory() for t in c] for c in cases]
+    outs = [torch.full((T, K), -5, dtype=torch.int32).pin_memory() for _ in cases]
+    events = [pipe.submit(*h, o) for h, o in zip(hosts, outs)]
+    for ev, o, w in zip(events, outs, want):
+        ev.synchronize()
+        assert torch.equal(o, w)
+    ops.check_status("cuda")
