@@ -32,9 +32,14 @@
 
 namespace dsa {
 
-constexpr int kTileKeys = 128;
+constexpr int kTileKeys = 128;         // keys per MMA (M); a paged work tile is two of these, see tile_keys()
 constexpr int kChunkTiles = 64;        // most key tiles per work unit (launches with few units use fewer)
 constexpr int kPageTokens = 64;
+// Keys per pipeline tile.  The paged (decode) form has one query token per sequence, so a 128-key tile is little
+// work (64 accumulator columns) against the fixed cost of its barrier hand-offs: it moves 256 keys (four pages)
+// per tile, as two M=128 MMAs into adjacent accumulator columns.
+template <bool PAGED>
+__host__ __device__ constexpr int tile_keys() { return PAGED ? 2 * kTileKeys : kTileKeys; }
 
 struct IndexerArgs {
   const float* k_scale;      // [S] (contiguous) or [num_pages*64] (paged), one per key
@@ -53,15 +58,29 @@ struct IndexerArgs {
   int* status;
 };
 
+// 4-byte asynchronous global -> shared copy (zero fill when !valid; src is then not read).  Unlike a load
+// into a register it leaves no scoreboard entry, so a prefetch several tiles ahead never stalls a later move.
+__device__ __forceinline__ void cp_async_f32(float* dst, const float* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 4 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int H, int D, int NQ, bool PAGED, int QB, int EPI>
 struct IdxCfg {
   static constexpr int N = H * NQ;                       // accumulator columns = (token, head) pairs
   static constexpr int NTOK = NQ * QB;                   // query tokens per work unit
   static constexpr int KSTEPS = D / 32;
-  static constexpr int K_TILE_BYTES = kTileKeys * D;
+  static constexpr int TILE_KEYS = tile_keys<PAGED>();
+  static constexpr int SUB = TILE_KEYS / kTileKeys;      // M=128 MMAs per tile
+  static constexpr int PAGES = TILE_KEYS / kPageTokens;  // cache pages per tile (paged)
+  static constexpr int ACC_COLS = N * SUB;               // accumulator columns per stage
+  static constexpr int K_TILE_BYTES = TILE_KEYS * D;
   static constexpr int Q_TILE_BYTES = N * D;
-  static constexpr int STAGES = PAGED ? 8 : 4;           // power of two: stage and phase come from shifts in the single-lane loops
-  static constexpr int TMEM_COLS = (2 * N < 32) ? 32 : 2 * N;
+  static constexpr int STAGES = PAGED ? 6 : 4;           // key tiles in flight (paged: 6 x 32 KB)
+  static constexpr int TMEM_COLS = (2 * ACC_COLS < 32) ? 32 : 2 * ACC_COLS;
   static constexpr uint64_t SWZ = (D == 128) ? kSwz128 : kSwz64;
   static constexpr uint32_t SBO = 8 * D;                 // 8 rows of D bytes
   static constexpr int EPI_WARPS = EPI * 4;
@@ -69,8 +88,10 @@ struct IdxCfg {
   static constexpr int SPLIT = EPI / 2;                  // warpgroups sharing one accumulator stage
   static constexpr int COLS_PER_WG = N / SPLIT;
   static constexpr int CH = 16;                          // columns per TMEM load
+  static constexpr int AHEAD = PAGED ? 4 : 2;            // key tiles by which the k_scale prefetch runs ahead
   static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * K_TILE_BYTES + 2 * QB * Q_TILE_BYTES +
-                                    2 * QB * N * 4 + 2 * NTOK * 8 + 256 + (PAGED ? 4 * kChunkTiles * 4 : 0);
+                                    2 * QB * N * 4 + 2 * NTOK * 8 + 256 + (PAGED ? 4 * PAGES * kChunkTiles * 4 : 0) +
+                                    AHEAD * SUB * EPI * 128 * 4;
   static_assert(EPI == 2 || EPI == 4, "two or four epilogue warpgroups");
   static_assert(N % 16 == 0 && N >= 16 && N <= 256, "MMA N out of range");
   static_assert(COLS_PER_WG % H == 0 && COLS_PER_WG % CH == 0, "a warpgroup must own whole tokens");
@@ -113,8 +134,9 @@ __device__ __forceinline__ bool unit_tiles(const IndexerArgs& a, int u, int n_qb
   int lo, hi;
   token_window<PAGED>(a, qb * QB * NQ, nb * NQ, lo, hi);
   if (hi <= lo) return false;
-  t_lo = max(c * a.chunk_tiles, lo / kTileKeys);
-  t_hi = min((c + 1) * a.chunk_tiles, (hi + kTileKeys - 1) / kTileKeys);
+  constexpr int TK = tile_keys<PAGED>();
+  t_lo = max(c * a.chunk_tiles, lo / TK);
+  t_hi = min((c + 1) * a.chunk_tiles, (hi + TK - 1) / TK);
   return t_lo < t_hi;
 }
 
@@ -197,7 +219,9 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   uint64_t* w_empty = w_full + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* pages_s = const_cast<int*>(abort_flag) + 1;            // paged: physical page of every page of the unit's chunk
+  int* pages_s = const_cast<int*>(abort_flag) + 1;            // paged: first cache row of every page of the unit's chunk, per producer
+  int* pagerow_s = pages_s + (PAGED ? 2 * C::PAGES * kChunkTiles : 0);   // paged: the same for the epilogue, 2 units deep (stager-written)
+  float* ks_ring = reinterpret_cast<float*>(pagerow_s + (PAGED ? 2 * C::PAGES * kChunkTiles : 0));   // AHEAD x SUB x epilogue threads
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -234,7 +258,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     // paged: warps 0 and 3 each take every other tile (the per-copy issue latency of two threads overlaps)
     constexpr int PL = PAGED ? 2 : 1;
     const int pidx = warp == 0 ? 0 : 1;
-    int* my_pages = pages_s + pidx * 2 * kChunkTiles;
+    int* my_pages = pages_s + pidx * C::PAGES * kChunkTiles;
     uint32_t it = 0, nu = 0;
     for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
       int qb, nb, t_lo, t_hi;
@@ -246,8 +270,8 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         // never waits on a dependent global load per tile
         const int n_pages = (min(a.ke[qb], a.S) + kPageTokens - 1) / kPageTokens;
         __syncwarp();
-        for (int i = lane; i < 2 * (t_hi - t_lo); i += 32) {   // store the first cache row of each page, -1 = none
-          const int page = 2 * t_lo + i;
+        for (int i = lane; i < C::PAGES * (t_hi - t_lo); i += 32) {   // store the first cache row of each page, -1 = none
+          const int page = C::PAGES * t_lo + i;
           int r = -1;
           if (page < n_pages) {
             const int phys = __ldg(a.block_table + (int64_t)qb * a.table_stride + page);
@@ -258,8 +282,6 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         __syncwarp();
       }
-      // Issuing a copy costs the issuing thread several hundred cycles of latency (barrier poll, expect_tx,
-      // copy), whatever its size.
       if (lane == 0 && pidx == 0) {
         ok = mbar_wait(&q_empty[qs], ((nu >> 1) & 1) ^ 1, abort_flag, a.status);
         if (ok) {
@@ -268,35 +290,34 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             tma_load_2d(q_s + (qs * QB + b) * C::Q_TILE_BYTES, &tmap_q, 0, (qb * QB + b) * C::N, &q_full[qs]);
         }
       }
-      if (lane == 0) {
-        for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
-          if (int(it % PL) != pidx) continue;
-          const int st = it % C::STAGES;
-          ok = mbar_wait(&k_empty[st], ((it / C::STAGES) & 1) ^ 1, abort_flag, a.status);
-          if (!ok) break;
-          uint8_t* dst = k_s + st * C::K_TILE_BYTES;
-          if constexpr (!PAGED) {
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      // The whole warp walks the tiles; lane 0 waits and posts the byte count.  Paged: lanes 0..3 then issue
+      // one page copy each in the same instruction, which costs the warp about what a single copy does.
+      for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
+        if (int(it % PL) != pidx) continue;
+        const int st = it % C::STAGES;
+        if (lane == 0) ok = mbar_wait(&k_empty[st], ((it / C::STAGES) & 1) ^ 1, abort_flag, a.status);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        uint8_t* dst = k_s + st * C::K_TILE_BYTES;
+        if constexpr (!PAGED) {
+          if (lane == 0) {
             mbar_expect_tx(&k_full[st], C::K_TILE_BYTES);
-            tma_load_2d(dst, &tmap_k, 0, kt * kTileKeys, &k_full[st]);
-          } else {
-            // two 64-token pages per tile; a missing or out-of-range page is skipped
-            const int2 rows2 = *reinterpret_cast<const int2*>(my_pages + 2 * (kt - t_lo));   // validated above
-            const int rows[2] = {rows2.x, rows2.y};
-            const uint32_t bytes = ((rows2.x >= 0) + (rows2.y >= 0)) * (C::K_TILE_BYTES / 2);
-            if (bytes) {
-              mbar_expect_tx(&k_full[st], bytes);
-#pragma unroll
-              for (int p = 0; p < 2; ++p)
-                if (rows[p] >= 0) tma_load_2d(dst + p * (C::K_TILE_BYTES / 2), &tmap_k, 0, rows[p], &k_full[st]);
-            } else {
-              mbar_arrive(&k_full[st]);
-            }
+            tma_load_2d(dst, &tmap_k, 0, kt * C::TILE_KEYS, &k_full[st]);
           }
+        } else {
+          // four 64-token pages per tile; a missing or out-of-range page is skipped (rows validated above)
+          const int r = lane < C::PAGES ? my_pages[C::PAGES * (kt - t_lo) + lane] : -1;
+          const int n_valid = __popc(__ballot_sync(0xffffffffu, r >= 0));
+          if (lane == 0) {
+            if (n_valid) mbar_expect_tx(&k_full[st], n_valid * (C::K_TILE_BYTES / C::PAGES));
+            else mbar_arrive(&k_full[st]);
+          }
+          __syncwarp();
+          if (r >= 0) tma_load_2d(dst + lane * (C::K_TILE_BYTES / C::PAGES), &tmap_k, 0, r, &k_full[st]);
         }
       }
       ++nu;
-      ok = __all_sync(0xffffffffu, ok);
-      it = __shfl_sync(0xffffffffu, it, 0) ;
       if (!ok) break;
     }
     // on abort, give copies already in flight a bounded chance to land
@@ -321,6 +342,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           const int st = it % C::STAGES;
           ok = mbar_wait(&k_full[st], (it / C::STAGES) & 1, abort_flag, a.status);
           const uint64_t kdesc = umma_smem_desc(smem_u32(k_s + st * C::K_TILE_BYTES), 16, C::SBO, C::SWZ);
+          constexpr uint32_t kSubDesc = (kTileKeys * D) >> 4;     // descriptor step from one 128-key half to the next
           for (int b = 0; b < nb && ok; ++b, ++it2) {
             const int acc = it2 & 1;
             ok = mbar_wait(&acc_empty[acc], ((it2 >> 1) & 1) ^ 1, abort_flag, a.status);
@@ -329,8 +351,11 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             const uint64_t qdesc =
                 umma_smem_desc(smem_u32(q_s + (qs * QB + b) * C::Q_TILE_BYTES), 16, C::SBO, C::SWZ);
 #pragma unroll
-            for (int k = 0; k < C::KSTEPS; ++k)
-              umma_f8(tmem_base + acc * C::N, kdesc + (k * 32 >> 4), qdesc + (k * 32 >> 4), idesc, k > 0);
+            for (int sub = 0; sub < C::SUB; ++sub)
+#pragma unroll
+              for (int k = 0; k < C::KSTEPS; ++k)
+                umma_f8(tmem_base + acc * C::ACC_COLS + sub * C::N, kdesc + sub * kSubDesc + (k * 32 >> 4),
+                        qdesc + (k * 32 >> 4), idesc, k > 0);
             umma_commit(&acc_full[acc]);
           }
           if (ok) umma_commit(&k_empty[st]);
@@ -374,6 +399,20 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         wind[j] = make_int2(s0, max(s1 - s0, 0));
       }
+      if constexpr (PAGED) {
+        // first cache row of each page of the chunk (-1 = none), so that the epilogue's k_scale fetch is one load
+        int* pr = pagerow_s + ub * C::PAGES * kChunkTiles;
+        const int n_pages = (min(a.ke[qb], a.S) + kPageTokens - 1) / kPageTokens;
+        for (int i = lane; i < C::PAGES * (t_hi - t_lo); i += 32) {
+          const int page = C::PAGES * t_lo + i;
+          int r = -1;
+          if (page < n_pages) {
+            const int phys = __ldg(a.block_table + (int64_t)qb * a.table_stride + page);
+            if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows) r = phys * kPageTokens;
+          }
+          pr[i] = r;
+        }
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&w_full[ub]);
       ++nu;
@@ -386,7 +425,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int part = wg >> 1;                    // which share of the columns (SPLIT > 1)
     const int wq = warp & 3;                     // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;              // key within the tile = TMEM lane
-    const uint32_t t_lane = tmem_base + (uint32_t(wq * 32) << 16) + stage * C::N;
+    const uint32_t t_lane = tmem_base + (uint32_t(wq * 32) << 16) + stage * C::ACC_COLS;
     uint32_t it2 = 0, n_mine = 0, nu = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
@@ -395,34 +434,41 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const int ub = nu & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(&w_full[ub], (nu >> 1) & 1, abort_flag, a.status));
       if (!ok) break;
-      auto load_kscale = [&](int tile) -> float {
-        const int sk = tile * kTileKeys + row;
-        if constexpr (!PAGED) {
-          return sk < a.S ? __ldg(a.k_scale + sk) : 0.f;
-        } else {
-          if (sk < min(a.ke[qb], a.S)) {
-            const int phys = __ldg(a.block_table + (int64_t)qb * a.table_stride + sk / kPageTokens);
-            if (phys >= 0 && (int64_t)(phys + 1) * kPageTokens <= a.num_phys_rows)
-              return __ldg(a.k_scale + (int64_t)phys * kPageTokens + (sk % kPageTokens));
+      // k_scale of the tile AHEAD tiles on travels global -> shared asynchronously into this thread's own slot
+      // (paged: its cache row comes from the page rows the stager wrote, so it is a single fetch)
+      float* my_ring = ks_ring + (threadIdx.x - 128);
+      const int* pr = pagerow_s + ub * C::PAGES * kChunkTiles;
+      auto prefetch_kscale = [&](int tile) {
+        if (tile < t_hi) {
+#pragma unroll
+          for (int sub = 0; sub < C::SUB; ++sub) {
+            const int sk = tile * C::TILE_KEYS + sub * kTileKeys + row;
+            const float* src = a.k_scale;
+            bool valid;
+            if constexpr (!PAGED) {
+              valid = sk < a.S;
+              if (valid) src += sk;
+            } else {
+              const int r = pr[C::PAGES * (tile - t_lo) + 2 * sub + (row >> 6)];
+              valid = r >= 0;
+              if (valid) src += r + (row & (kPageTokens - 1));
+            }
+            cp_async_f32(my_ring + ((tile % C::AHEAD) * C::SUB + sub) * (EPI * 128), src, valid);
           }
-          return 0.f;
         }
+        cp_async_commit();                       // one group per tile, empty past the end of the unit
       };
       const uint32_t ld32 = static_cast<uint32_t>(a.ld);
-      // k_scale is requested ahead of the math: one key tile for contiguous keys, four for the paged
-      // cache, where it takes two dependent loads (page id, then scale) and tiles are short
-      constexpr int AHEAD = PAGED ? 4 : 1;
-      float ksq[AHEAD];
 #pragma unroll
-      for (int i = 0; i < AHEAD; ++i) ksq[i] = load_kscale(min(t_lo + i, t_hi - 1));
+      for (int i = 0; i < C::AHEAD; ++i) prefetch_kscale(t_lo + i);
       for (int kt = t_lo; kt < t_hi && ok; ++kt) {
-        const float kscale = ksq[0];
+        cp_async_wait<C::AHEAD - 1>();           // this tile's group has landed
+        float kscale[C::SUB];
 #pragma unroll
-        for (int i = 0; i + 1 < AHEAD; ++i) ksq[i] = ksq[i + 1];
-        ksq[AHEAD - 1] = load_kscale(min(kt + AHEAD, t_hi - 1));
+        for (int sub = 0; sub < C::SUB; ++sub) kscale[sub] = my_ring[((kt % C::AHEAD) * C::SUB + sub) * (EPI * 128)];
+        prefetch_kscale(kt + C::AHEAD);          // reuses the slots just read
         for (int b = 0; b < nb; ++b, ++it2) {
           if (int(it2 & 1) != stage) continue;
-          const int s = kt * kTileKeys + row;    // logical key position
           const int g = qb * QB + b;
           const float* my_w = w_s + (ub * QB + b) * C::N;
           const int2* my_win = win_s + ub * C::NTOK + b * NQ;
@@ -431,15 +477,20 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[stage], n_mine & 1, abort_flag, a.status));
           if (!ok) break;
           tc_fence_after();
-          if constexpr (C::SPLIT == 1) {
-            drain_columns<H, NQ, C::CH, 0, C::N>(t_lane, my_w, my_win, kscale, s, s < a.S, n_tok, grp_base, ld32);
-          } else {
-            if (part == 0)
-              drain_columns<H, NQ, C::CH, 0, C::COLS_PER_WG>(t_lane, my_w, my_win, kscale, s, s < a.S, n_tok,
-                                                             grp_base, ld32);
-            else
-              drain_columns<H, NQ, C::CH, C::COLS_PER_WG, C::COLS_PER_WG>(t_lane, my_w, my_win, kscale, s,
-                                                                          s < a.S, n_tok, grp_base, ld32);
+#pragma unroll
+          for (int sub = 0; sub < C::SUB; ++sub) {
+            const int s = kt * C::TILE_KEYS + sub * kTileKeys + row;    // logical key position
+            const uint32_t t_sub = t_lane + sub * C::N;
+            if constexpr (C::SPLIT == 1) {
+              drain_columns<H, NQ, C::CH, 0, C::N>(t_sub, my_w, my_win, kscale[sub], s, s < a.S, n_tok, grp_base, ld32);
+            } else {
+              if (part == 0)
+                drain_columns<H, NQ, C::CH, 0, C::COLS_PER_WG>(t_sub, my_w, my_win, kscale[sub], s, s < a.S, n_tok,
+                                                               grp_base, ld32);
+              else
+                drain_columns<H, NQ, C::CH, C::COLS_PER_WG, C::COLS_PER_WG>(t_sub, my_w, my_win, kscale[sub], s,
+                                                                            s < a.S, n_tok, grp_base, ld32);
+            }
           }
           tc_fence_before();
           __syncwarp();
@@ -447,6 +498,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           ++n_mine;
         }
       }
+      cp_async_wait<0>();                        // nothing of this unit may land in a slot of the next
       __syncwarp();
       if (lane == 0) mbar_arrive(&w_empty[ub]);
       ++nu;
@@ -538,7 +590,7 @@ static int launch_indexer(const void* q, const void* k, const IndexerArgs& args,
   if (rc) return rc;
   const int n_groups = (a.T + NQ - 1) / NQ;
   const int n_qblocks = (n_groups + QB - 1) / QB;
-  const int n_tiles = (a.S + kTileKeys - 1) / kTileKeys;
+  const int n_tiles = (a.S + C::TILE_KEYS - 1) / C::TILE_KEYS;
   // Units are dealt to the CTAs round-robin: keep at least six rounds of them so that the last, partly
   // filled round costs little, by cutting the key range finer when there are few query blocks.
   a.chunk_tiles = kChunkTiles;
