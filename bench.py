@@ -474,8 +474,8 @@ def main():
     achieved = flops / (k_ms * 1e-3) / 1e12
     peak_fp8 = 2.0 * peaks["bf16_tflops"]
     # dram__bytes_read + dram__bytes_write of the indexer kernel from one ncu capture of the 512-row reduced
-    # case (13.84 MB + 75.25 MB), scaled by the row count (traffic is proportional to query rows)
-    traffic = (13.84e6 + 75.25e6) * T_ROWS / 512
+    # case (13.04 MB read + 75.74 MB written), scaled by the row count (traffic is proportional to query rows)
+    traffic = (13.04e6 + 75.74e6) * T_ROWS / 512
     topk_bytes = 4.0 * causal_keys + T_ROWS * TOPK * 4
 
     line = {
