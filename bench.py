@@ -218,6 +218,23 @@ def extra_measurements(dev, peaks):
         "note": "positions drawn with replacement (timing only); the kernel computes Q.K^T twice per token (one CTA per V half)"}
     del q, kv, idx, o
     torch.cuda.empty_cache()
+    # ---- block-sparse MHA: the reference's register_sparse_fa().run shape (its PART B) -------------
+    from llmdivedeep_b200 import DSA as dsa_mod
+    build_lut, run = dsa_mod.register_sparse_fa()
+    rows_bs = []
+    for S_bs, ref_ms in ((8192, 0.12), (16384, 0.36), (32768, 1.23)):
+        qb_, kb_, vb_ = (torch.randn(1, S_bs, 24, 128, device=dev, dtype=torch.bfloat16, generator=g) for _ in range(3))
+        lut, num, topk_b = build_lut(qb_, S_bs, 0.05)
+        ms = _time_ms(lambda: run(qb_, kb_, vb_, lut, num, 128 ** -0.5), iters=10)
+        rows_bs.append({"seq_len": S_bs, "key_blocks_per_query_block": topk_b, "ms": ms,
+                        "tflops": 4.0 * 24 * S_bs * topk_b * 64 * 128 / ms / 1e9,
+                        "reference_published_ms": ref_ms, "speedup": ref_ms / ms})
+        del qb_, kb_, vb_, lut, num
+    out["block_sparse_mha"] = {
+        "what": "[1, S, 24, 128] bf16, 64-token blocks, 5 % of the key blocks per query block, non-causal: the shape of "
+                "the reference's block-sparse stand-in (its README table, one B200, an external Triton kernel)",
+        "rows": rows_bs}
+    torch.cuda.empty_cache()
     # ---- one decode step --------------------------------------------------------------
     B, CTX = 64, 131072
     P = CTX // 64

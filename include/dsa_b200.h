@@ -119,6 +119,18 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_fp8, const float* k_scale,
 int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_t* idx, void* out_bf16, int T, int H,
                            int S_kv, int K, float scale, int32_t* status, void* stream);
 
+/* Block-sparse multi-head attention, the call behind register_sparse_fa().run
+ * (sparse_attn/DSA.py:232-247: triton_block_sparse_attn_fwd_openai_prefetch(q, k, v, idx, num,
+ * sm_scale) -> (out, _), whose source is not part of the reference).  Non-causal; 64-token blocks:
+ *   out[b,s,h,:] = softmax_j(scale * q[b,s,h,:] . k[b,j,h,:]) v[b,j,h,:],  j over the key blocks
+ *   lut[b,h,s/64,0..num[b,h,s/64]) of query block s/64.
+ *   q, k, v, out [B, S, H, 128] bf16, contiguous, 16-byte aligned; S a multiple of 64;
+ *   lut [B, H, S/64, topk] int32 key-block ids (an id outside [0, S/64) contributes nothing and
+ *   sets status 2); num [B, H, S/64] int32, clamped to [0, min(topk, 1024)]. */
+int dsa_block_sparse_mha(const void* q_bf16, const void* k_bf16, const void* v_bf16, const int32_t* lut,
+                         const int32_t* num, void* out_bf16, int B, int S, int H, int D, int topk, float scale,
+                         int32_t* status, void* stream);
+
 /* The same attention for decode over the paged FP8 latent cache (no counterpart
  * in the reference, which has no cache: sparse_attn/DSA.py:475-477).  One query
  * token per sequence; idx[b, j] is a logical position of sequence b, stored at

@@ -92,10 +92,25 @@ def register_dense_fn() -> Optional[Callable]:
 
 
 def register_sparse_fa() -> Optional[Tuple[Callable, Callable]]:
-    """The block-sparse MHA stand-in of the reference ([B,S,24,128], 64-token blocks) is not
-    built; the sparse step of this package is token-sparse MLA (``SparseMLA``).  Returning None
-    makes the reference drivers skip their PART B/D rows, as they do without the backend."""
-    return None
+    """(build_lut, run) like the reference (sparse_attn/DSA.py:208-249), with `run` on this package's
+    block-sparse MHA kernel ([B,S,H,128] bf16, 64-token blocks, non-causal) instead of the external Triton
+    kernel the reference imports.  build_lut draws a random per-query-block list the same way (:232-241)."""
+    if not torch.cuda.is_available():
+        return None
+
+    def build_lut(q: torch.Tensor, S: int, sparsity: float) -> Tuple[torch.Tensor, torch.Tensor, int]:
+        B, _, H, _ = q.shape
+        Nq = Nkv = S // SPARSE_BLOCK
+        topk = max(1, int(round(sparsity * Nkv)))
+        scores = torch.rand(B, H, Nq, Nkv, device=q.device)
+        idx = scores.topk(topk, dim=-1).indices.to(torch.int32).contiguous()
+        q2k_num = torch.full((B, H, Nq), topk, dtype=torch.int32, device=q.device)
+        return idx, q2k_num, topk
+
+    def run(q, k, v, idx, num, sm_scale):
+        return ops.block_sparse_attn(q, k, v, idx, num, sm_scale)
+
+    return build_lut, run
 
 
 # ---- kernel-level simulator (reference: sparse_attn/DSA.py:256-362) ---------------------------------

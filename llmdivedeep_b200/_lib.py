@@ -32,6 +32,8 @@ SIGNATURES = {
                                  c_int, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "dsa_sparse_mla_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                                        c_void_p, c_void_p]),
+    "dsa_block_sparse_mha": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                     c_int, c_int, c_float, c_void_p, c_void_p]),
     "dsa_sparse_mla_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "dsa_sparse_mla_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),

@@ -56,6 +56,9 @@ int sparse_mla_decode_launch(const void* q, const void* cache, const int32_t* bl
                              float scale, void* workspace, size_t workspace_bytes, int32_t* status,
                              cudaStream_t stream);
 size_t mla_decode_workspace_bytes(int B, int H, int K);
+int block_sparse_mha_launch(const void* q, const void* k, const void* v, const int32_t* lut, const int32_t* num,
+                            void* out, int B, int S, int H, int topk, float scale, int32_t* status,
+                            cudaStream_t stream);
 
 int fp8_quant_launch(const void* x, int x_is_bf16, int64_t n_blocks, int block, void* q, float* scale,
                      cudaStream_t stream);
@@ -142,6 +145,24 @@ int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_
   if (K > 2048) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: K (%d) exceeds 2048 selected keys per query", K);
   return sparse_mla_prefill_launch(q_bf16, kv_bf16, idx, out_bf16, T, H, S_kv, K, scale, status,
                                    static_cast<cudaStream_t>(stream));
+}
+
+int dsa_block_sparse_mha(const void* q_bf16, const void* k_bf16, const void* v_bf16, const int32_t* lut,
+                         const int32_t* num, void* out_bf16, int B, int S, int H, int D, int topk, float scale,
+                         int32_t* status, void* stream) {
+  g_err[0] = 0;
+  if (B < 0 || S < 0 || H < 0 || topk < 0) return set_error(DSA_ERR_SHAPE, "block_sparse_mha: negative size");
+  if (D != 128) return set_error(DSA_ERR_SHAPE, "block_sparse_mha: head dim %d, only 128 is built", D);
+  if (S % 64) return set_error(DSA_ERR_SHAPE, "block_sparse_mha: S (%d) must be a multiple of the 64-token block", S);
+  if (B == 0 || S == 0 || H == 0) return DSA_OK;
+  if (!q_bf16 || !k_bf16 || !v_bf16 || !out_bf16 || !num || (topk > 0 && !lut))
+    return set_error(DSA_ERR_ARG, "block_sparse_mha: NULL pointer argument");
+  if (!aligned16(q_bf16) || !aligned16(k_bf16) || !aligned16(v_bf16) || !aligned16(out_bf16))
+    return set_error(DSA_ERR_ALIGN, "block_sparse_mha: q, k, v and out must be 16-byte aligned");
+  if ((int64_t)B * S > 0x7fffffffLL || H > 65535 || B > 65535)
+    return set_error(DSA_ERR_SHAPE, "block_sparse_mha: B*S, H or B too large");
+  return block_sparse_mha_launch(q_bf16, k_bf16, v_bf16, lut, num, out_bf16, B, S, H, topk, scale, status,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int32_t* block_table,

@@ -225,6 +225,27 @@ def sparse_mla_prefill(q, kv, idx, scale: float, out: Optional[torch.Tensor] = N
     return out
 
 
+def block_sparse_attn(q, k, v, lut, num, sm_scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Block-sparse multi-head attention with the reference's stand-in signature (sparse_attn/DSA.py:232-247):
+    q, k, v [B, S, H, 128] bf16; lut [B, H, S/64, topk] int32 key-block ids per 64-row query block;
+    num [B, H, S/64] int32 = how many entries of each list count.  Non-causal.  Returns bf16 [B, S, H, 128]."""
+    _need_cuda(q, k, v, lut, num)
+    if any(t.dtype != torch.bfloat16 for t in (q, k, v)) or lut.dtype != torch.int32 or num.dtype != torch.int32:
+        raise DsaError("block_sparse_attn takes bf16 q/k/v and int32 lut/num")
+    if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
+        raise DsaError(f"bad shapes q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)}")
+    B, S, H, D = q.shape
+    if lut.dim() != 4 or tuple(lut.shape[:3]) != (B, H, S // 64) or tuple(num.shape) != (B, H, S // 64):
+        raise DsaError(f"bad shapes lut {tuple(lut.shape)} num {tuple(num.shape)} for q {tuple(q.shape)}")
+    q, k, v, lut, num = q.contiguous(), k.contiguous(), v.contiguous(), lut.contiguous(), num.contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    lib = _lib.load()
+    check(lib.dsa_block_sparse_mha(_ptr(q), _ptr(k), _ptr(v), _ptr(lut), _ptr(num), _ptr(out), B, S, H, D,
+                                   lut.shape[3], float(sm_scale), _ptr(status_word(q.device)), _stream()))
+    return out
+
+
 def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: Optional[int] = None,
                             out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode step over the paged FP8 latent cache.  q [B,H,576] bf16, cache uint8

@@ -394,3 +394,29 @@ def dsa_layer_forward(params, x, q_lora, q_mla, kv, n_heads, head_dim, rope_dim,
     # on -inf entries); the sparse step must ignore them.
     idx32 = torch.where(idx < ke, idx, torch.full_like(idx, -1)).to(torch.int32)
     return idx32, sparse_mla(q_mla, kv, idx32, scale)
+
+
+def block_sparse_mha(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, lut: torch.Tensor, num: torch.Tensor,
+                     sm_scale: float, block: int = 64) -> torch.Tensor:
+    """Block-sparse multi-head attention, the arithmetic behind register_sparse_fa().run
+    (sparse_attn/DSA.py:232-247; the Triton kernel it calls is not part of the reference, so this restates
+    the published semantics of that call: non-causal softmax attention of every 64-row query block over the
+    key blocks its list names).  q, k, v [B, S, H, D]; lut [B, H, S/block, topk]; num [B, H, S/block].
+    fp32 arithmetic; returns fp32 [B, S, H, D].  Parity unpinned: the reference holds no vectors for it."""
+    B, S, H, D = q.shape
+    nqb = S // block
+    qf, kf, vf = q.float(), k.float(), v.float()
+    out = torch.zeros(B, S, H, D, dtype=torch.float32)
+    for b in range(B):
+        for h in range(H):
+            for qb in range(nqb):
+                n = int(num[b, h, qb])
+                ids = [int(i) for i in lut[b, h, qb, :n].tolist() if 0 <= int(i) < nqb]
+                if not ids:
+                    continue
+                cols = torch.cat([torch.arange(i * block, (i + 1) * block) for i in ids])
+                qs = qf[b, qb * block:(qb + 1) * block, h]                  # [block, D]
+                sc = (qs @ kf[b, cols, h].T) * sm_scale                      # [block, n*block]
+                p = torch.softmax(sc, dim=-1)
+                out[b, qb * block:(qb + 1) * block, h] = p @ vf[b, cols, h]
+    return out

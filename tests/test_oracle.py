@@ -166,3 +166,18 @@ def test_check_topk_sets_rules():
     assert O.check_topk_sets(np.array([[1, 0, 5]]), sc, [0], [2], 3)["bad_rows"] == [0]
     tie = np.array([[1, 1, 1, 0]], dtype=np.float32)
     assert O.check_topk_sets(np.array([[3 - 1, 0]]), tie, [0], [4], 2)["exact_rows"] == 1
+
+
+def test_block_sparse_oracle_with_every_block_listed_is_full_attention():
+    """The block-sparse MHA restatement reduces to plain softmax attention when every key block is listed."""
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(1, 256, 2, 128, generator=g) for _ in range(3))
+    nb = 4
+    lut = torch.arange(nb, dtype=torch.int32).expand(1, 2, nb, nb).contiguous()
+    num = torch.full((1, 2, nb), nb, dtype=torch.int32)
+    got = O.block_sparse_mha(q, k, v, lut, num, 128 ** -0.5)
+    full = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2),
+                                                            v.transpose(1, 2)).transpose(1, 2)
+    assert float((got - full).abs().max()) < 1e-5
+    num[0, 1, 2] = 0
+    assert float(O.block_sparse_mha(q, k, v, lut, num, 0.1)[0, 128:192, 1].abs().max()) == 0.0
