@@ -30,11 +30,13 @@ constexpr int kBsBlk = 64;                         // tokens per query / key blo
 constexpr int kBsD = 128;                          // head dim
 constexpr int kBsPanelBytes = kBsBlk * 128;        // [64 rows x 64 dims] bf16
 constexpr int kBsTileBytes = 2 * kBsPanelBytes;    // [64 rows x 128 dims]
-constexpr int kBsStages = 2;
+constexpr int kBsKStages = 3;                      // K tiles in flight: a K stage is free once its scores are computed
+constexpr int kBsVStages = 2;                      // V tiles in flight: needed one softmax later, freed after P.V
 constexpr int kBsThreads = 256;
 constexpr int kBsMaxList = 1024;                   // listed key blocks per query block held in shared memory
-constexpr int kBsSmemBytes = 1024 + kBsTileBytes /*Q*/ + kBsStages * 2 * kBsTileBytes /*K,V*/ + kBsPanelBytes /*P*/ +
-                             256 /*barriers*/ + kBsMaxList * 4;
+constexpr int kBsSmemBytes = 1024 + kBsTileBytes /*Q*/ + (kBsKStages + kBsVStages) * kBsTileBytes /*K,V*/ +
+                             kBsPanelBytes /*P*/ + 256 /*barriers*/ + kBsMaxList * 4;
+static_assert(2 * kBsSmemBytes <= 227 * 1024, "two CTAs per SM");
 constexpr uint32_t kBsColO = 0, kBsColS = 128, kBsTmemCols = 256;
 
 struct BsArgs {
@@ -64,18 +66,20 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;                                        // 2 panels [64 rows x 128 B]
   uint8_t* k_s = q_s + kBsTileBytes;                          // stages x 2 panels
-  uint8_t* v_s = k_s + kBsStages * kBsTileBytes;              // stages x 2 panels
-  uint8_t* p_s = v_s + kBsStages * kBsTileBytes;              // [64 rows x 64 keys] bf16, one panel
+  uint8_t* v_s = k_s + kBsKStages * kBsTileBytes;             // stages x 2 panels
+  uint8_t* p_s = v_s + kBsVStages * kBsTileBytes;             // [64 rows x 64 keys] bf16, one panel
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kBsPanelBytes);
   uint64_t* q_full = bars + 0;
   uint64_t* o_final = bars + 1;
-  uint64_t* kv_full = bars + 2;                               // [2] TMA -> MMA
-  uint64_t* kv_free = bars + 4;                               // [2] P.V of the block finished
-  uint64_t* s_full = bars + 6;                                // MMA -> softmax
-  uint64_t* s_free = bars + 7;                                // softmax has read S
-  uint64_t* p_full = bars + 8;                                // softmax -> MMA
-  uint64_t* pv_done = bars + 9;                               // [2] P.V of block j finished: O quiescent, P free
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_full = bars + 2;                                // [3] TMA -> MMA
+  uint64_t* k_free = bars + 5;                                // [3] the scores of the block are computed
+  uint64_t* v_full = bars + 8;                                // [2] TMA -> MMA
+  uint64_t* v_free = bars + 10;                               // [2] P.V of the block finished
+  uint64_t* s_full = bars + 12;                               // MMA -> softmax
+  uint64_t* s_free = bars + 13;                               // softmax has read S
+  uint64_t* p_full = bars + 14;                               // softmax -> MMA
+  uint64_t* pv_done = bars + 15;                              // [2] P.V of block j finished: O quiescent, P free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* lut_s = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
@@ -88,9 +92,13 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     mbar_init(o_final, 1);
+    for (int i = 0; i < kBsKStages; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_free[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_free[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_free[i], 1);
       mbar_init(&pv_done[i], 1);
     }
     mbar_init(s_full, 1);
@@ -128,21 +136,39 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   const int x0 = h * (kBsD / 2);                              // TMA x coordinate in 4-byte units: head h, dim 0
 
   if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+    // ------------------------------ K producer (and Q) ------------------------------
+    // The whole warp walks the list; lane 0 waits and posts the byte count, then lanes 0 and 1 issue the two
+    // panel copies in one instruction (a copy costs its issuing thread several hundred cycles whatever its size).
     if (lane == 0) {
       mbar_expect_tx(q_full, kBsTileBytes);
       for (int p = 0; p < 2; ++p)
         tma_load_2d(q_s + p * kBsPanelBytes, &tmap_q, x0 + p * 32, b * a.S + qb * kBsBlk, q_full);
-      for (int j = 0; j < n; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_free[st], ((j >> 1) & 1) ^ 1, abort_flag, a.status)) break;
-        const int kb = max(lut_s[j], 0);                      // a bad entry reads block 0 (defined data); its scores are masked
-        mbar_expect_tx(&kv_full[st], 2 * kBsTileBytes);
-        for (int p = 0; p < 2; ++p) {
-          tma_load_2d(k_s + st * kBsTileBytes + p * kBsPanelBytes, &tmap_k, x0 + p * 32, b * a.S + kb * kBsBlk, &kv_full[st]);
-          tma_load_2d(v_s + st * kBsTileBytes + p * kBsPanelBytes, &tmap_v, x0 + p * 32, b * a.S + kb * kBsBlk, &kv_full[st]);
-        }
-      }
+    }
+    bool ok = true;
+    for (int j = 0; j < n && ok; ++j) {
+      const int st = j % kBsKStages;
+      if (lane == 0) ok = mbar_wait(&k_free[st], ((j / kBsKStages) & 1) ^ 1, abort_flag, a.status);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      const int kb = max(lut_s[j], 0);                        // a bad entry reads block 0 (defined data); its scores are masked
+      if (lane == 0) mbar_expect_tx(&k_full[st], kBsTileBytes);
+      __syncwarp();
+      if (lane < 2)
+        tma_load_2d(k_s + st * kBsTileBytes + lane * kBsPanelBytes, &tmap_k, x0 + lane * 32, b * a.S + kb * kBsBlk, &k_full[st]);
+    }
+  } else if (warp == 2) {
+    // --------------------------------- V producer ---------------------------------
+    bool ok = true;
+    for (int j = 0; j < n && ok; ++j) {
+      const int st = j & 1;
+      if (lane == 0) ok = mbar_wait(&v_free[st], ((j >> 1) & 1) ^ 1, abort_flag, a.status);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      const int kb = max(lut_s[j], 0);
+      if (lane == 0) mbar_expect_tx(&v_full[st], kBsTileBytes);
+      __syncwarp();
+      if (lane < 2)
+        tma_load_2d(v_s + st * kBsTileBytes + lane * kBsPanelBytes, &tmap_v, x0 + lane * 32, b * a.S + kb * kBsBlk, &v_full[st]);
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
@@ -156,8 +182,8 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       constexpr uint64_t kStage = kBsTileBytes >> 4, kPanel = kBsPanelBytes >> 4;
       bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
       auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, a.status)) return false;
+        const int st = j % kBsKStages;
+        if (!mbar_wait(&k_full[st], (j / kBsKStages) & 1, abort_flag, a.status)) return false;
         if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, a.status)) return false;
         tc_fence_after();
 #pragma unroll
@@ -167,24 +193,25 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             umma_f16_ss(tmem + kBsColS, qdesc + p * kPanel + 2 * ks, kdesc0 + st * kStage + p * kPanel + 2 * ks, idesc_qk,
                         (p | ks) != 0);
         umma_commit(s_full);
+        umma_commit(&k_free[st]);
         return true;
       };
       if (ok) ok = issue_qk(0);
       for (int j = 0; j < n && ok; ++j) {
         const int st = j & 1;
         bool qk_done = j + 1 >= n;
-        if (!qk_done && mbar_try_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) {   // next scores while this softmax runs
+        if (!qk_done && mbar_try_wait(&k_full[(j + 1) % kBsKStages], ((j + 1) / kBsKStages) & 1)) {   // next scores while this softmax runs
           ok = issue_qk(j + 1);
           qk_done = true;
         }
         if (!ok) break;
-        ok = mbar_wait(p_full, j & 1, abort_flag, a.status);
+        ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, a.status) && mbar_wait(p_full, j & 1, abort_flag, a.status);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kBsBlk / 16; ++ks)      // 16 keys per step: 32 B along P's rows, 16 rows x 128 B into each V panel
           umma_f16_ss(tmem + kBsColO, pdesc + 2 * ks, vdesc0 + st * kStage + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
-        umma_commit(&kv_free[st]);
+        umma_commit(&v_free[st]);
         umma_commit(&pv_done[j & 1]);
         if (j == n - 1) umma_commit(o_final);
         if (!qk_done) ok = issue_qk(j + 1);
