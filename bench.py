@@ -517,13 +517,13 @@ def main():
                     "topk_select_gbs": topk_bytes / (topk_ms * 1e-3) / 1e9,
                     "topk_select_frac_of_hbm": topk_bytes / (topk_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     }
-    if not args.no_extra and args.rows == 4096:
+    if not args.no_extra and args.rows == 4096 and world == 1:
         del sets, host_sets, pipe, ws, logits
         torch.cuda.empty_cache()
         line["extra"] = extra_measurements(dev, peaks)
     if sharded is not None:
         line.setdefault("extra", {})["sparse_mla_prefill_sharded"] = sharded
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:            # the CPU leg is timed at N=1 only
         rows = 512
         cpu_port_rows_per_s(16)
         v, secs, cores = cpu_port_rows_per_s(rows)
