@@ -535,6 +535,270 @@ __global__ void fill_masked_kernel(const IndexerArgs a) {
   for (int s = s_hi + threadIdx.x; s < a.S; s += blockDim.x) row[s] = -CUDART_INF_F;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Register-weight form for 64 heads x 128 dims over contiguous keys (the prefill shape).
+// The epilogue of the general kernel is bound by delivering head weights from shared memory: every thread
+// needs all 256 weights of a tile, 128 KB per tile through a 128 B/clk port.  Here a tile is still 128 keys x
+// (4 query tokens x 64 heads), but each of FOUR epilogue warpgroups owns ONE token of the group: its 64
+// weights stay in registers (32 packed pairs) for the whole work unit, and per tile a thread walks only the
+// 64 accumulator columns of its token.  No shared-memory traffic in the inner loop at all.  The price: a unit
+// holds one query group (not two), so a key tile fetched from L2 serves 4 query tokens instead of 8.
+// Summation order per (token, key) is the same as in the general kernel: the two forms agree bit for bit.
+struct RwCfg {
+  static constexpr int H = 64, D = 128, NQ = 4, N = 256, KSTEPS = 4;
+  static constexpr int K_TILE_BYTES = kTileKeys * D, Q_TILE_BYTES = N * D;
+  static constexpr int STAGES = 6;
+  static constexpr int EPI_WG = 4, EPI_WARPS = 16, THREADS = 128 + EPI_WG * 128;
+  static constexpr int AHEAD = 2;
+  static constexpr uint32_t SBO = 8 * D;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * K_TILE_BYTES + 2 * Q_TILE_BYTES + 2 * N * 4 + 2 * NQ * 8 + 256 +
+                                    AHEAD * EPI_WG * 128 * 4;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+__global__ void __launch_bounds__(RwCfg::THREADS, 1)
+indexer_logits_rw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const IndexerArgs a, const int n_groups, const int n_units) {
+  using C = RwCfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k_s = smem;                                        // STAGES x [128 keys x D]
+  uint8_t* q_s = k_s + C::STAGES * C::K_TILE_BYTES;           // 2 x [N rows x D]
+  float* w_s = reinterpret_cast<float*>(q_s + 2 * C::Q_TILE_BYTES);   // 2 x N head weights
+  int2* win_s = reinterpret_cast<int2*>(w_s + 2 * C::N);              // 2 x NQ (ks, ke - ks)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(win_s + 2 * C::NQ);
+  uint64_t* k_full = bars;                  // [STAGES]
+  uint64_t* k_empty = k_full + C::STAGES;   // [STAGES]
+  uint64_t* q_full = k_empty + C::STAGES;   // [2]
+  uint64_t* q_empty = q_full + 2;           // [2]
+  uint64_t* acc_full = q_empty + 2;         // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint64_t* w_full = acc_empty + 2;         // [2]
+  uint64_t* w_empty = w_full + 2;           // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* ks_ring = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // AHEAD x epilogue threads
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::STAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], C::EPI_WARPS);     // every epilogue warp drains a share of every stage
+      mbar_init(&w_full[i], 1);
+      mbar_init(&w_empty[i], C::EPI_WARPS);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    uint32_t it = 0, nu = 0;
+    for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
+      int g, nb, t_lo, t_hi;
+      if (!unit_tiles<C::NQ, 1, false>(a, u, n_groups, n_groups, g, nb, t_lo, t_hi)) continue;
+      const int qs = nu & 1;
+      bool ok = true;
+      if (lane == 0) {
+        ok = mbar_wait(&q_empty[qs], ((nu >> 1) & 1) ^ 1, abort_flag, a.status);
+        if (ok) {
+          mbar_expect_tx(&q_full[qs], C::Q_TILE_BYTES);
+          tma_load_2d(q_s + qs * C::Q_TILE_BYTES, &tmap_q, 0, g * C::N, &q_full[qs]);
+        }
+        for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
+          const int st = it % C::STAGES;
+          ok = mbar_wait(&k_empty[st], ((it / C::STAGES) & 1) ^ 1, abort_flag, a.status);
+          if (!ok) break;
+          mbar_expect_tx(&k_full[st], C::K_TILE_BYTES);
+          tma_load_2d(k_s + st * C::K_TILE_BYTES, &tmap_k, 0, kt * kTileKeys, &k_full[st]);
+        }
+      }
+      ++nu;
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      it = __shfl_sync(0xffffffffu, it, 0);
+      if (!ok) break;
+    }
+    if (lane == 0 && *abort_flag) {               // on abort, give copies already in flight a bounded chance to land
+      for (int st = 0; st < C::STAGES; ++st)
+        for (uint32_t spin = 0; spin < (1u << 16) && !mbar_try_wait(&k_full[st], 0) && !mbar_try_wait(&k_full[st], 1); ++spin) {
+        }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    constexpr uint32_t idesc = umma_idesc(0, 0, 0, 0, kTileKeys, C::N);
+    uint32_t it = 0, nu = 0;
+    for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
+      int g, nb, t_lo, t_hi;
+      if (!unit_tiles<C::NQ, 1, false>(a, u, n_groups, n_groups, g, nb, t_lo, t_hi)) continue;
+      const int qs = nu & 1;
+      bool ok = true;
+      if (lane == 0) {
+        ok = mbar_wait(&q_full[qs], (nu >> 1) & 1, abort_flag, a.status);
+        const uint64_t qdesc = umma_smem_desc(smem_u32(q_s + qs * C::Q_TILE_BYTES), 16, C::SBO, kSwz128);
+        for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
+          const int st = it % C::STAGES, acc = it & 1;
+          ok = mbar_wait(&k_full[st], (it / C::STAGES) & 1, abort_flag, a.status) &&
+               mbar_wait(&acc_empty[acc], ((it >> 1) & 1) ^ 1, abort_flag, a.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t kdesc = umma_smem_desc(smem_u32(k_s + st * C::K_TILE_BYTES), 16, C::SBO, kSwz128);
+#pragma unroll
+          for (int k = 0; k < C::KSTEPS; ++k)
+            umma_f8(tmem_base + acc * C::N, kdesc + (k * 32 >> 4), qdesc + (k * 32 >> 4), idesc, k > 0);
+          umma_commit(&acc_full[acc]);
+          umma_commit(&k_empty[st]);
+        }
+        if (ok) umma_commit(&q_empty[qs]);
+      }
+      ++nu;
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      it = __shfl_sync(0xffffffffu, it, 0);
+      if (!ok) break;
+    }
+  } else if (warp == 2) {
+    // ------------------- stager: head weights and windows of the next unit -------------------
+    uint32_t nu = 0;
+    for (int u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
+      int g, nb, t_lo, t_hi;
+      if (!unit_tiles<C::NQ, 1, false>(a, u, n_groups, n_groups, g, nb, t_lo, t_hi)) continue;
+      const int ub = nu & 1;
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(&w_empty[ub], ((nu >> 1) & 1) ^ 1, abort_flag, a.status));
+      if (!ok) break;
+      float* wd = w_s + ub * C::N;
+      const int t0 = g * C::NQ;
+      for (int c = lane; c < C::N; c += 32) {
+        const int t = t0 + c / C::H;
+        float wvv = 0.f;
+        if (t < a.T) {
+          const int64_t off = (int64_t)t * C::H + (c % C::H);
+          wvv = a.w_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[off])
+                            : reinterpret_cast<const float*>(a.w)[off];
+        }
+        wd[c] = wvv;
+      }
+      if (lane < C::NQ) {
+        const int t = t0 + lane;
+        int s0 = 0, s1 = 0;
+        if (t < a.T) {
+          s0 = a.ks ? max(a.ks[t], 0) : 0;
+          s1 = min(a.ke[t], a.S);
+        }
+        win_s[ub * C::NQ + lane] = make_int2(s0, max(s1 - s0, 0));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&w_full[ub]);
+      ++nu;
+    }
+  } else if (warp >= 4) {
+    // ------------- epilogue: warpgroup = query token of the group, thread = key of the tile -------------
+    const int ew = warp - 4;
+    const int tok = ew >> 2;                     // token within the group = 64-column slice of the accumulator
+    const int wq = warp & 3;                     // TMEM lane quadrant of this warp
+    const int row = wq * 32 + lane;              // key within the tile = TMEM lane
+    const uint32_t t_lane = tmem_base + (uint32_t(wq * 32) << 16) + tok * C::H;
+    float* my_ring = ks_ring + (threadIdx.x - 128);
+    uint32_t it = 0, nu = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+      int g, nb, t_lo, t_hi;
+      if (!unit_tiles<C::NQ, 1, false>(a, u, n_groups, n_groups, g, nb, t_lo, t_hi)) continue;
+      const int ub = nu & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&w_full[ub], (nu >> 1) & 1, abort_flag, a.status));
+      if (!ok) break;
+      uint64_t wreg[C::H / 2];                   // this token's 64 head weights as 32 packed pairs, for the whole unit
+      {
+        const float4* src = reinterpret_cast<const float4*>(w_s + ub * C::N + tok * C::H);
+#pragma unroll
+        for (int i = 0; i < C::H / 4; ++i) {
+          const float4 w4 = src[i];
+          wreg[2 * i] = pack_f32x2(w4.x, w4.y);
+          wreg[2 * i + 1] = pack_f32x2(w4.z, w4.w);
+        }
+      }
+      const int2 win = win_s[ub * C::NQ + tok];  // (ks, ke - ks)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&w_empty[ub]);  // weights and window are in registers
+      const int t_tok = g * C::NQ + tok;
+      float* out_row = a.logits + (int64_t)t_tok * a.ld;
+      auto prefetch_kscale = [&](int tile) {
+        if (tile < t_hi) {
+          const int sk = tile * kTileKeys + row;
+          cp_async_f32(my_ring + (tile % C::AHEAD) * (C::EPI_WG * 128), a.k_scale + (sk < a.S ? sk : 0), sk < a.S);
+        }
+        cp_async_commit();
+      };
+#pragma unroll
+      for (int i = 0; i < C::AHEAD; ++i) prefetch_kscale(t_lo + i);
+      for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
+        const int stage = it & 1;
+        cp_async_wait<C::AHEAD - 1>();
+        const float kscale = my_ring[(kt % C::AHEAD) * (C::EPI_WG * 128)];
+        prefetch_kscale(kt + C::AHEAD);
+        ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[stage], (it >> 1) & 1, abort_flag, a.status));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t_acc = t_lane + stage * C::N;
+        uint32_t v[2][16];
+        uint64_t chain[2];
+        tmem_ld16(t_acc, v[0]);
+#pragma unroll
+        for (int c = 0; c < C::H; c += 16) {
+          const int cur = (c >> 4) & 1;
+          tmem_wait_ld();
+          if (c + 16 < C::H) tmem_ld16(t_acc + c + 16, v[cur ^ 1]);
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const int hp = (c + i) >> 1;               // head pair
+            const float d0 = fmaxf(__uint_as_float(v[cur][i]), 0.f);
+            const float d1 = fmaxf(__uint_as_float(v[cur][i + 1]), 0.f);
+            if (hp < 2) chain[hp] = 0;
+            chain[hp & 1] = fma_f32x2(pack_f32x2(d0, d1), wreg[hp], chain[hp & 1]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[stage]);   // the accumulator slice is in registers
+        float e0, o0, e1, o1;
+        unpack_f32x2(chain[0], e0, o0);
+        unpack_f32x2(chain[1], e1, o1);
+        const float score = (0.f + (e0 + o0)) + (e1 + o1);
+        const int s = kt * kTileKeys + row;              // key position
+        if (s < a.S && t_tok < a.T) {
+          const bool in = static_cast<uint32_t>(s - win.x) < static_cast<uint32_t>(win.y);
+          out_row[s] = in ? score * kscale : -CUDART_INF_F;
+        }
+      }
+      cp_async_wait<0>();
+      ++nu;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------- host side ----------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -612,9 +876,38 @@ static int launch_indexer(const void* q, const void* k, const IndexerArgs& args,
   return check_launch("indexer_logits");
 }
 
+
+static int launch_indexer_rw(const void* q, const void* k, const IndexerArgs& args, int clean, cudaStream_t stream) {
+  using C = RwCfg;
+  if (args.T == 0 || args.S == 0) return DSA_OK;
+  IndexerArgs a = args;
+  CUtensorMap tq, tk;
+  int rc = make_tmap_2d_u8(&tq, q, (uint64_t)a.T * C::H, C::D, C::D, C::N);
+  if (rc) return rc;
+  rc = make_tmap_2d_u8(&tk, k, (uint64_t)a.S, C::D, C::D, kTileKeys);
+  if (rc) return rc;
+  const int n_groups = (a.T + C::NQ - 1) / C::NQ;
+  const int n_tiles = (a.S + kTileKeys - 1) / kTileKeys;
+  a.chunk_tiles = kChunkTiles;                      // same rule as the general form: at least six rounds of units
+  while (a.chunk_tiles > 8 && (int64_t)n_groups * ((n_tiles + a.chunk_tiles - 1) / a.chunk_tiles) < 6LL * sm_count())
+    a.chunk_tiles /= 2;
+  const int64_t n_units64 = (int64_t)n_groups * ((n_tiles + a.chunk_tiles - 1) / a.chunk_tiles);
+  if (n_units64 > 0x7fffffff) return set_error(DSA_ERR_SHAPE, "indexer: too many work units");
+  const int n_units = (int)n_units64;
+  if (cudaFuncSetAttribute(indexer_logits_rw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+    return set_error(DSA_ERR_CUDA, "indexer: cannot raise dynamic shared memory to %d", C::SMEM_BYTES);
+  const int grid = n_units < sm_count() ? n_units : sm_count();
+  indexer_logits_rw_kernel<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tq, tk, a, n_groups, n_units);
+  if (clean) fill_masked_kernel<C::NQ><<<a.T, 256, 0, stream>>>(a);
+  return check_launch("indexer_logits");
+}
+
 int indexer_logits_dispatch(const void* q, const void* k, const IndexerArgs& a, int H, int D, int clean,
                             cudaStream_t stream) {
   static const bool epi4 = getenv("DSA_IDX_EPI4") != nullptr;
+  // DSA_IDX_RW=0 keeps 64 x 128 on the general kernel (used to compare the two forms)
+  static const bool rw = !(getenv("DSA_IDX_RW") && getenv("DSA_IDX_RW")[0] == '0');
+  if (H == 64 && D == 128 && rw && !epi4) return launch_indexer_rw(q, k, a, clean, stream);
 #define DSA_IDX_CASE(h, d)                                                                \
   if (H == h && D == d) {                                                                 \
     if (epi4) return launch_indexer<h, d, 256 / h, false, 2, 4>(q, k, a, clean, stream);  \
