@@ -491,8 +491,8 @@ def main():
     achieved = flops / (k_ms * 1e-3) / 1e12
     peak_fp8 = 2.0 * peaks["bf16_tflops"]
     # dram__bytes_read + dram__bytes_write of the indexer kernel from one ncu capture of the 512-row reduced
-    # case (13.04 MB read + 75.74 MB written), scaled by the row count (traffic is proportional to query rows)
-    traffic = (13.04e6 + 75.74e6) * T_ROWS / 512
+    # case (13.32 MB read + 76.51 MB written), scaled by the row count (traffic is proportional to query rows)
+    traffic = (13.32e6 + 76.51e6) * T_ROWS / 512
     topk_bytes = 4.0 * causal_keys + T_ROWS * TOPK * 4
 
     line = {
@@ -509,7 +509,7 @@ def main():
                        "region ends after the last step's device -> host copy"},
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "indexer_logits_kernel<64,128,4>", "achieved": achieved,
+        "roofline": {"bound": "tensor", "kernel": "indexer_logits_rw_kernel (64 heads x 128, 4 query tokens per tile)", "achieved": achieved,
                      "peak": peak_fp8, "unit": "TFLOP/s", "frac": achieved / peak_fp8, "traffic": traffic,
                      "peak_source": f"2 x bf16_tflops (burst, kernel timed alone) of {peak_kind} peaks: fp8 e4m3 dense = 2x bf16; no fp8 entry is recorded",
                      "ms_per_launch": k_ms, "flops_per_launch": flops},
@@ -524,11 +524,11 @@ def main():
     if sharded is not None:
         line.setdefault("extra", {})["sparse_mla_prefill_sharded"] = sharded
     if not args.no_cpu_baseline and world == 1:            # the CPU leg is timed at N=1 only
-        rows = 512
+        rows = 4096                                        # one whole step of the workload: about 15 s of CPU work
         cpu_port_rows_per_s(16)
         v, secs, cores = cpu_port_rows_per_s(rows)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                "sample": f"last {rows} of the 4096 query rows, full 65536 keys, {secs:.1f} s; "
+                                "sample": f"all {rows} query rows of one step, full 65536 keys, {secs:.1f} s; "
                                           "CPU oracle port (fp32 fallback arithmetic + ReLU, row-chunked) + torch.topk"}
     print(json.dumps(line))
     if world > 1:
