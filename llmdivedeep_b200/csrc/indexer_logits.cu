@@ -906,7 +906,8 @@ int indexer_logits_dispatch(const void* q, const void* k, const IndexerArgs& a, 
                             cudaStream_t stream) {
   static const bool epi4 = getenv("DSA_IDX_EPI4") != nullptr;
   // DSA_IDX_RW=0 keeps 64 x 128 on the general kernel (used to compare the two forms)
-  static const bool rw = !(getenv("DSA_IDX_RW") && getenv("DSA_IDX_RW")[0] == '0');
+  const char* rw_env = getenv("DSA_IDX_RW");            // read per call: tests switch it to compare the two forms
+  const bool rw = !(rw_env && rw_env[0] == '0');
   if (H == 64 && D == 128 && rw && !epi4) return launch_indexer_rw(q, k, a, clean, stream);
 #define DSA_IDX_CASE(h, d)                                                                \
   if (H == h && D == d) {                                                                 \

@@ -178,3 +178,20 @@ def test_host_pipeline_submits_back_to_back():
         ev.synchronize()
         assert torch.equal(o, w)
     ops.check_status("cuda")
+
+
+@pytest.mark.parametrize("T,S,window", [(300, 4096, "causal"), (1021, 9000, "random"), (64, 70000, "causal")])
+def test_register_weight_form_equals_general_kernel_bitwise(T, S, window):
+    """64 heads x 128 takes the register-weight kernel; DSA_IDX_RW=0 sends the same call through the general
+    kernel.  Same summation order per (token, key): the logits agree bit for bit, for fp32 and bf16 weights."""
+    import os
+    q8, k8, ksc, w, ks, ke = to_dev(*indexer_inputs(T, S, 64, 128, seed=T + S, window=window))
+    for wt in (w, w.bfloat16()):
+        a = ops.fp8_mqa_logits(q8, (k8, ksc), wt, ks, ke).clone()
+        os.environ["DSA_IDX_RW"] = "0"
+        try:
+            b = ops.fp8_mqa_logits(q8, (k8, ksc), wt, ks, ke).clone()
+        finally:
+            os.environ.pop("DSA_IDX_RW", None)
+        assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+    ops.check_status("cuda")
