@@ -281,6 +281,15 @@ def run_profile_case(args):
         o = torch.empty(T, H, 512, dtype=torch.bfloat16, device=dev)
         ms = _time_ms(lambda: ops.sparse_mla_prefill(q, kv, idx, 192 ** -0.5, out=o), iters=max(1, args.steps), warm=args.warmup)
         info = {"tokens": T, "ms": ms, "tflops_algorithmic": 2.0 * H * 1088 * T * K / ms / 1e9}
+    elif args.case == "block_sparse_small":
+        from llmdivedeep_b200 import DSA as dsa_mod
+        S = 8192                                           # q, k, v: 3 x 50 MB
+        q, k, v = (torch.randn(1, S, 24, 128, device=dev, dtype=torch.bfloat16, generator=g) for _ in range(3))
+        build_lut, run = dsa_mod.register_sparse_fa()
+        lut, num, topk_b = build_lut(q, S, 0.05)
+        ms = _time_ms(lambda: run(q, k, v, lut, num, 128 ** -0.5), iters=max(1, args.steps), warm=args.warmup)
+        info = {"seq_len": S, "key_blocks_per_query_block": topk_b, "ms": ms,
+                "tflops": 4.0 * 24 * S * topk_b * 64 * 128 / ms / 1e9}
     else:
         B, CTX = 8, 131072
         P = CTX // 64
@@ -355,7 +364,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the secondary measurements (sparse MLA prefill, decode step)")
-    ap.add_argument("--case", default="headline", choices=["headline", "mla_prefill_small", "decode_small"],
+    ap.add_argument("--case", default="headline", choices=["headline", "mla_prefill_small", "decode_small", "block_sparse_small"],
                     help="anything but 'headline' runs a few launches of a reduced case for profiler captures and "
                          "prints a line marked as such, not a bench value")
     ap.add_argument("--rows", type=int, default=T_ROWS,
