@@ -5,11 +5,13 @@
 // block, the key blocks it attends to (the first num[b, h, qb] entries count); non-causal.
 //   out[b, s, h, :] = softmax_j(scale * q[b, s, h, :] . k[b, j, h, :]) v[b, j, h, :],  j over the listed blocks
 //
-// One CTA per (batch, head, query block); two CTAs share an SM.  A query block is 64 rows, so the MMAs
-// are M = 64: their accumulator rows sit in lanes 0-15 of each 32-lane quadrant of tensor memory, and
-// each of the four softmax warps works on 16 rows.
-//   * warp 0 lane 0: TMA producer.  Q [64 x 128] once, then per listed key block K and V [64 x 128]
-//     each as two 128-byte-swizzled panels of 64 dims, into a two-stage ring.
+// Persistent CTAs, two per SM, each walking units (batch, head, query block).  A query block is 64 rows, so
+// the MMAs are M = 64: their accumulator rows sit in lanes 0-15 of each 32-lane quadrant of tensor memory,
+// and each of the four softmax warps works on 16 rows.  Barrier stages and phases follow from running
+// counters, so the producers load the next unit's Q, K and V while the current unit is still in its tail.
+//   * warps 0 and 2: TMA producers (Q and K; V).  Q [64 x 128] once per unit, then per listed key block K and
+//     V [64 x 128], each as two 128-byte-swizzled panels of 64 dims, into a 3-stage K ring and a 2-stage V ring;
+//     32 list entries are read at a time, one per lane.
 //   * warp 1: owns the tensor memory; lane 0 issues S = Q K^T (8 tcgen05.mma kind::f16, K-major
 //     operands) and O += P V (4 MMAs; P from shared memory, V read through an MN-major descriptor, so
 //     the [key][dim] tile needs no transpose).
@@ -33,9 +35,8 @@ constexpr int kBsTileBytes = 2 * kBsPanelBytes;    // [64 rows x 128 dims]
 constexpr int kBsKStages = 3;                      // K tiles in flight: a K stage is free once its scores are computed
 constexpr int kBsVStages = 2;                      // V tiles in flight: needed one softmax later, freed after P.V
 constexpr int kBsThreads = 256;
-constexpr int kBsMaxList = 1024;                   // listed key blocks per query block held in shared memory
 constexpr int kBsSmemBytes = 1024 + kBsTileBytes /*Q*/ + (kBsKStages + kBsVStages) * kBsTileBytes /*K,V*/ +
-                             kBsPanelBytes /*P*/ + 256 /*barriers*/ + kBsMaxList * 4;
+                             kBsPanelBytes /*P*/ + 256 /*barriers*/;
 static_assert(2 * kBsSmemBytes <= 227 * 1024, "two CTAs per SM");
 constexpr uint32_t kBsColO = 0, kBsColS = 128, kBsTmemCols = 256;
 
@@ -61,7 +62,7 @@ __device__ __forceinline__ float bs_exp2(float x) {
 
 __global__ void __launch_bounds__(kBsThreads, 2)
 block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                        const __grid_constant__ CUtensorMap tmap_v, const BsArgs a) {
+                        const __grid_constant__ CUtensorMap tmap_v, const BsArgs a, const int n_units) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;                                        // 2 panels [64 rows x 128 B]
@@ -69,8 +70,8 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   uint8_t* v_s = k_s + kBsKStages * kBsTileBytes;             // stages x 2 panels
   uint8_t* p_s = v_s + kBsVStages * kBsTileBytes;             // [64 rows x 64 keys] bf16, one panel
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kBsPanelBytes);
-  uint64_t* q_full = bars + 0;
-  uint64_t* o_final = bars + 1;
+  uint64_t* q_full = bars + 0;                                // TMA -> MMA, once per unit
+  uint64_t* q_empty = bars + 1;                               // the unit's last scores are issued: Q may be replaced
   uint64_t* k_full = bars + 2;                                // [3] TMA -> MMA
   uint64_t* k_free = bars + 5;                                // [3] the scores of the block are computed
   uint64_t* v_full = bars + 8;                                // [2] TMA -> MMA
@@ -78,20 +79,21 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   uint64_t* s_full = bars + 12;                               // MMA -> softmax
   uint64_t* s_free = bars + 13;                               // softmax has read S
   uint64_t* p_full = bars + 14;                               // softmax -> MMA
-  uint64_t* pv_done = bars + 15;                              // [2] P.V of block j finished: O quiescent, P free
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* pv_done = bars + 15;                              // [2] P.V of a block finished: O quiescent, P free
+  uint64_t* o_final = bars + 17;                              // the unit's last P.V finished
+  uint64_t* o_free = bars + 18;                               // the unit's O has been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* lut_s = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int nkb = a.S / kBsBlk;
-  const int64_t unit = ((int64_t)b * a.H + h) * a.nqb + qb;
-  const int n = min(max(a.num[unit], 0), min(a.topk, kBsMaxList));
+  const int list_cap = a.topk;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     mbar_init(o_final, 1);
+    mbar_init(o_free, 128);
     for (int i = 0; i < kBsKStages; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_free[i], 1);
@@ -110,21 +112,6 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  for (int j = threadIdx.x; j < n; j += kBsThreads) {         // the list, validated once
-    int kb = a.lut[unit * a.topk + j];
-    if (kb < 0 || kb >= nkb) {
-      if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
-      kb = -1;                                                // its scores are masked: contributes nothing
-    }
-    lut_s[j] = kb;
-  }
-  if (n == 0) {                                               // nothing listed: zero rows
-    if (threadIdx.x < kBsBlk) {
-      uint4* o = reinterpret_cast<uint4*>(a.out + (((int64_t)b * a.S + qb * kBsBlk + threadIdx.x) * a.H + h) * kBsD);
-      for (int c = 0; c < kBsD * 2 / 16; ++c) o[c] = make_uint4(0, 0, 0, 0);
-    }
-    return;
-  }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kBsTmemCols);
     tmem_relinquish();
@@ -133,42 +120,72 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const int x0 = h * (kBsD / 2);                              // TMA x coordinate in 4-byte units: head h, dim 0
 
-  if (warp == 0) {
-    // ------------------------------ K producer (and Q) ------------------------------
-    // The whole warp walks the list; lane 0 waits and posts the byte count, then lanes 0 and 1 issue the two
-    // panel copies in one instruction (a copy costs its issuing thread several hundred cycles whatever its size).
-    if (lane == 0) {
-      mbar_expect_tx(q_full, kBsTileBytes);
-      for (int p = 0; p < 2; ++p)
-        tma_load_2d(q_s + p * kBsPanelBytes, &tmap_q, x0 + p * 32, b * a.S + qb * kBsBlk, q_full);
-    }
+  // A CTA walks units u = blockIdx.x, blockIdx.x + gridDim.x, ...; unit = (batch, head, query block), query block
+  // fastest, so that neighbouring CTAs share K/V blocks in L2.  Every role walks the same sequence and keeps its own
+  // running counters (units with a non-empty list: nq; key blocks: jt), from which barrier stages and phases follow;
+  // the producers run ahead into the next unit while the current one is still being worked on.
+  auto unit_len = [&](int u) { return min(max(__ldg(a.num + u), 0), list_cap); };
+  auto decode = [&](int u, int& b, int& h, int& qb) {
+    qb = u % a.nqb;
+    const int bh = u / a.nqb;
+    h = bh % a.H;
+    b = bh / a.H;
+  };
+
+  if (warp == 0 || warp == 2) {
+    // ----------- TMA producers: warp 0 = Q and K, warp 2 = V.  The whole warp walks the lists; lane 0 waits and
+    // posts the byte count, lanes 0 and 1 issue the two panel copies of a tile in one instruction. -----------
+    const bool is_k = warp == 0;
+    uint32_t nq = 0, jt = 0;
     bool ok = true;
-    for (int j = 0; j < n && ok; ++j) {
-      const int st = j % kBsKStages;
-      if (lane == 0) ok = mbar_wait(&k_free[st], ((j / kBsKStages) & 1) ^ 1, abort_flag, a.status);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      const int kb = max(lut_s[j], 0);                        // a bad entry reads block 0 (defined data); its scores are masked
-      if (lane == 0) mbar_expect_tx(&k_full[st], kBsTileBytes);
-      __syncwarp();
-      if (lane < 2)
-        tma_load_2d(k_s + st * kBsTileBytes + lane * kBsPanelBytes, &tmap_k, x0 + lane * 32, b * a.S + kb * kBsBlk, &k_full[st]);
-    }
-  } else if (warp == 2) {
-    // --------------------------------- V producer ---------------------------------
-    bool ok = true;
-    for (int j = 0; j < n && ok; ++j) {
-      const int st = j & 1;
-      if (lane == 0) ok = mbar_wait(&v_free[st], ((j >> 1) & 1) ^ 1, abort_flag, a.status);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      const int kb = max(lut_s[j], 0);
-      if (lane == 0) mbar_expect_tx(&v_full[st], kBsTileBytes);
-      __syncwarp();
-      if (lane < 2)
-        tma_load_2d(v_s + st * kBsTileBytes + lane * kBsPanelBytes, &tmap_v, x0 + lane * 32, b * a.S + kb * kBsBlk, &v_full[st]);
+    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+      const int n = unit_len(u);
+      if (n == 0) continue;
+      int b, h, qb;
+      decode(u, b, h, qb);
+      const int x0 = h * (kBsD / 2);                          // TMA x coordinate in 4-byte units: head h, dim 0
+      if (is_k) {
+        if (lane == 0) {
+          ok = mbar_wait(q_empty, (nq & 1) ^ 1, abort_flag, a.status);
+          if (ok) mbar_expect_tx(q_full, kBsTileBytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        if (lane < 2) tma_load_2d(q_s + lane * kBsPanelBytes, &tmap_q, x0 + lane * 32, b * a.S + qb * kBsBlk, q_full);
+      }
+      const int32_t* list = a.lut + (int64_t)u * a.topk;
+      for (int j0 = 0; j0 < n && ok; j0 += 32) {
+        int e = (j0 + lane < n) ? __ldg(list + j0 + lane) : 0;     // 32 list entries at a time, one per lane
+        if (e < 0 || e >= nkb) {
+          if (is_k && a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+          e = 0;                                              // a bad entry reads block 0 (defined data); its scores are masked
+        }
+        const int jn = min(32, n - j0);
+        for (int jj = 0; jj < jn && ok; ++jj, ++jt) {
+          const int kb = __shfl_sync(0xffffffffu, e, jj);
+          if (is_k) {
+            const int st = jt % kBsKStages;
+            if (lane == 0) ok = mbar_wait(&k_free[st], ((jt / kBsKStages) & 1) ^ 1, abort_flag, a.status);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(&k_full[st], kBsTileBytes);
+            __syncwarp();
+            if (lane < 2)
+              tma_load_2d(k_s + st * kBsTileBytes + lane * kBsPanelBytes, &tmap_k, x0 + lane * 32, b * a.S + kb * kBsBlk, &k_full[st]);
+          } else {
+            const int st = jt & 1;
+            if (lane == 0) ok = mbar_wait(&v_free[st], ((jt >> 1) & 1) ^ 1, abort_flag, a.status);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(&v_full[st], kBsTileBytes);
+            __syncwarp();
+            if (lane < 2)
+              tma_load_2d(v_s + st * kBsTileBytes + lane * kBsPanelBytes, &tmap_v, x0 + lane * 32, b * a.S + kb * kBsBlk, &v_full[st]);
+          }
+        }
+      }
+      ++nq;
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
@@ -180,11 +197,12 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const uint64_t kdesc0 = umma_smem_desc(smem_u32(k_s), 16, 1024, kSwz128);
       const uint64_t vdesc0 = umma_smem_desc(smem_u32(v_s), kBsPanelBytes, 1024, kSwz128);
       constexpr uint64_t kStage = kBsTileBytes >> 4, kPanel = kBsPanelBytes >> 4;
-      bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
-      auto issue_qk = [&](int j) -> bool {
-        const int st = j % kBsKStages;
-        if (!mbar_wait(&k_full[st], (j / kBsKStages) & 1, abort_flag, a.status)) return false;
-        if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, a.status)) return false;
+      uint32_t nq = 0, jt = 0;                                // jt: blocks whose scores have been issued... of finished units
+      bool ok = true;
+      auto issue_qk = [&](uint32_t t) -> bool {               // scores of running block t
+        const int st = t % kBsKStages;
+        if (!mbar_wait(&k_full[st], (t / kBsKStages) & 1, abort_flag, a.status)) return false;
+        if (t > 0 && !mbar_wait(s_free, (t - 1) & 1, abort_flag, a.status)) return false;
         tc_fence_after();
 #pragma unroll
         for (int p = 0; p < 2; ++p)
@@ -196,25 +214,39 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         umma_commit(&k_free[st]);
         return true;
       };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < n && ok; ++j) {
-        const int st = j & 1;
-        bool qk_done = j + 1 >= n;
-        if (!qk_done && mbar_try_wait(&k_full[(j + 1) % kBsKStages], ((j + 1) / kBsKStages) & 1)) {   // next scores while this softmax runs
-          ok = issue_qk(j + 1);
-          qk_done = true;
-        }
-        if (!ok) break;
-        ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, a.status) && mbar_wait(p_full, j & 1, abort_flag, a.status);
-        if (!ok) break;
-        tc_fence_after();
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        const int n = unit_len(u);
+        if (n == 0) continue;
+        ok = mbar_wait(q_full, nq & 1, abort_flag, a.status);
+        if (ok) ok = issue_qk(jt);
+        if (ok && n == 1) umma_commit(q_empty);
+        if (ok && nq > 0) ok = mbar_wait(o_free, (nq - 1) & 1, abort_flag, a.status);   // the previous unit's O is read out
+        for (int j = 0; j < n && ok; ++j) {
+          const uint32_t t = jt + j;
+          const int st = t & 1;
+          bool qk_done = j + 1 >= n;
+          if (!qk_done && mbar_try_wait(&k_full[(t + 1) % kBsKStages], ((t + 1) / kBsKStages) & 1)) {   // next scores while this softmax runs
+            ok = issue_qk(t + 1);
+            if (ok && j + 2 == n) umma_commit(q_empty);       // those were the unit's last scores
+            qk_done = true;
+          }
+          if (!ok) break;
+          ok = mbar_wait(&v_full[st], (t >> 1) & 1, abort_flag, a.status) && mbar_wait(p_full, t & 1, abort_flag, a.status);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < kBsBlk / 16; ++ks)      // 16 keys per step: 32 B along P's rows, 16 rows x 128 B into each V panel
-          umma_f16_ss(tmem + kBsColO, pdesc + 2 * ks, vdesc0 + st * kStage + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
-        umma_commit(&v_free[st]);
-        umma_commit(&pv_done[j & 1]);
-        if (j == n - 1) umma_commit(o_final);
-        if (!qk_done) ok = issue_qk(j + 1);
+          for (int ks = 0; ks < kBsBlk / 16; ++ks)    // 16 keys per step: 32 B along P's rows, 16 rows x 128 B into each V panel
+            umma_f16_ss(tmem + kBsColO, pdesc + 2 * ks, vdesc0 + st * kStage + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
+          umma_commit(&v_free[st]);
+          umma_commit(&pv_done[t & 1]);
+          if (j == n - 1) umma_commit(o_final);
+          if (!qk_done) {
+            ok = issue_qk(t + 1);
+            if (ok && j + 2 == n) umma_commit(q_empty);
+          }
+        }
+        jt += n;
+        ++nq;
       }
     }
   } else if (warp >= 4) {
@@ -223,77 +255,89 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     const bool active = lane < 16;
     const int row = quad * 16 + (lane & 15);                  // query row of the block (lanes 16-31 shadow lanes 0-15)
     const uint32_t t_row = tmem + (uint32_t(quad * 32) << 16);
-    float m = -CUDART_INF_F, l = 0.f;
+    uint32_t nq = 0, jt = 0;
     bool ok = true;
-    for (int j = 0; j < n && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, a.status));
+    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+      const int n = unit_len(u);
+      int b, h, qb;
+      decode(u, b, h, qb);
+      __nv_bfloat16* orow = a.out + (((int64_t)b * a.S + qb * kBsBlk + row) * a.H + h) * kBsD;
+      if (n == 0) {                                           // nothing listed: zero rows
+        if (active)
+          for (int c = 0; c < kBsD * 2 / 16; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0, 0, 0, 0);
+        continue;
+      }
+      const int32_t* list = a.lut + (int64_t)u * a.topk;
+      float m = -CUDART_INF_F, l = 0.f;
+      for (int j = 0; j < n && ok; ++j, ++jt) {
+        const int kb = __ldg(list + j);                       // requested before the wait: only its validity is needed
+        ok = __all_sync(0xffffffffu, mbar_wait(s_full, jt & 1, abort_flag, a.status));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sv[kBsBlk];
+        tmem_ld32(t_row + kBsColS, *reinterpret_cast<uint32_t(*)[32]>(sv));
+        tmem_ld32(t_row + kBsColS + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(s_free);
+        const bool listed = kb >= 0 && kb < nkb;
+        float s[kBsBlk];
+        float bmax = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < kBsBlk; ++i) {
+          s[i] = (listed && active) ? __uint_as_float(sv[i]) * a.scale_log2e : -CUDART_INF_F;
+          bmax = fmaxf(bmax, s[i]);
+        }
+        const float m_new = fmaxf(m, bmax);
+        const bool grow = m_new - m > 8.f;             // also true when m is still -inf and m_new is finite
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? bs_exp2(m - m_new) : 1.f;
+          if (grow) m = m_new;
+          l *= alpha;
+          if (j > 0) {                                 // O must be quiescent: P.V of the previous block complete
+            ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(jt - 1) & 1], ((jt - 1) >> 1) & 1, abort_flag, a.status));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < kBsD; c += 32) {
+              uint32_t ov[32];
+              tmem_ld32(t_row + kBsColO + c, ov);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              tmem_st32(t_row + kBsColO + c, ov);
+            }
+            tmem_wait_st();
+          }
+        }
+        const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+        uint32_t pk[kBsBlk / 2];
+        float psum = 0.f;
+#pragma unroll
+        for (int i = 0; i < kBsBlk; i += 2) {
+          const float p0 = bs_exp2(s[i] - m_eff), p1 = bs_exp2(s[i + 1] - m_eff);
+          psum += p0 + p1;
+          pk[i >> 1] = bs_pack_bf16x2(p0, p1);
+        }
+        l += psum;
+        if (jt > 0) {                                  // P is single-buffered: P.V of the previous block (of any unit) must be done
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(jt - 1) & 1], ((jt - 1) >> 1) & 1, abort_flag, a.status));
+          if (!ok) break;
+        }
+        if (active) {                                  // this row of P: 128 bytes, K-major, 128-byte swizzle
+          uint8_t* dst = p_s + row * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        }
+        fence_async_smem();                            // visible to the tensor core's reads
+        tc_fence_before();
+        mbar_arrive(p_full);
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, nq & 1, abort_flag, a.status));
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[kBsBlk];
-      tmem_ld32(t_row + kBsColS, *reinterpret_cast<uint32_t(*)[32]>(sv));
-      tmem_ld32(t_row + kBsColS + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(s_free);
-      const bool listed = lut_s[j] >= 0;
-      float s[kBsBlk];
-      float bmax = -CUDART_INF_F;
-#pragma unroll
-      for (int i = 0; i < kBsBlk; ++i) {
-        s[i] = (listed && active) ? __uint_as_float(sv[i]) * a.scale_log2e : -CUDART_INF_F;
-        bmax = fmaxf(bmax, s[i]);
-      }
-      const float m_new = fmaxf(m, bmax);
-      const bool grow = m_new - m > 8.f;               // also true when m is still -inf and m_new is finite
-      if (__any_sync(0xffffffffu, grow)) {
-        const float alpha = grow ? bs_exp2(m - m_new) : 1.f;
-        if (grow) m = m_new;
-        l *= alpha;
-        if (j > 0) {                                   // O must be quiescent: P.V of the previous block complete
-          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll 1
-          for (int c = 0; c < kBsD; c += 32) {
-            uint32_t ov[32];
-            tmem_ld32(t_row + kBsColO + c, ov);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st32(t_row + kBsColO + c, ov);
-          }
-          tmem_wait_st();
-        }
-      }
-      const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-      uint32_t pk[kBsBlk / 2];
-      float psum = 0.f;
-#pragma unroll
-      for (int i = 0; i < kBsBlk; i += 2) {
-        const float p0 = bs_exp2(s[i] - m_eff), p1 = bs_exp2(s[i + 1] - m_eff);
-        psum += p0 + p1;
-        pk[i >> 1] = bs_pack_bf16x2(p0, p1);
-      }
-      l += psum;
-      if (j > 0) {                                     // P is single-buffered: P.V of the previous block must be done
-        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
-        if (!ok) break;
-      }
-      if (active) {                                    // this row of P: 128 bytes, K-major, 128-byte swizzle
-        uint8_t* dst = p_s + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      }
-      fence_async_smem();                              // visible to the tensor core's reads
-      tc_fence_before();
-      mbar_arrive(p_full);
-    }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
-    if (ok) {
-      tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = a.out + (((int64_t)b * a.S + qb * kBsBlk + row) * a.H + h) * kBsD;
 #pragma unroll 1
       for (int c = 0; c < kBsD; c += 32) {
         uint32_t ov[32];
@@ -311,6 +355,9 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(o_free);                             // the next unit's first P.V may overwrite O
+      ++nq;
     }
   }
 
@@ -342,8 +389,11 @@ int block_sparse_mha_launch(const void* q, const void* k, const void* v, const i
   a.status = status;
   if (cudaFuncSetAttribute(block_sparse_mha_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBsSmemBytes) != cudaSuccess)
     return set_error(DSA_ERR_CUDA, "block_sparse_mha: cannot raise dynamic shared memory to %d", kBsSmemBytes);
-  const dim3 grid(a.nqb, H, B);
-  block_sparse_mha_kernel<<<grid, kBsThreads, kBsSmemBytes, stream>>>(tq, tk, tv, a);
+  const int64_t n_units64 = (int64_t)B * H * a.nqb;
+  if (n_units64 > 0x7fffffff) return set_error(DSA_ERR_SHAPE, "block_sparse_mha: too many query blocks");
+  const int n_units = (int)n_units64;
+  const int grid = n_units < 2 * sm_count() ? n_units : 2 * sm_count();   // persistent: two CTAs per SM
+  block_sparse_mha_kernel<<<grid, kBsThreads, kBsSmemBytes, stream>>>(tq, tk, tv, a, n_units);
   return check_launch("block_sparse_mha");
 }
 
