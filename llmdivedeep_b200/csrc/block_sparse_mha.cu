@@ -281,13 +281,19 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         tc_fence_before();
         mbar_arrive(s_free);
         const bool listed = kb >= 0 && kb < nkb;
-        float s[kBsBlk];
+        // An M = 64 accumulator keeps its rows in lanes 0-15 of the quadrant, so lanes 16-31 would idle (and
+        // pay for 64 exponentials of garbage).  Each row is split instead: lane r keeps columns 0-31, lane
+        // r + 16 receives columns 32-63 by shuffle; maximum and sum are combined across the pair.
+        float s[kBsBlk / 2];
         float bmax = -CUDART_INF_F;
 #pragma unroll
-        for (int i = 0; i < kBsBlk; ++i) {
-          s[i] = (listed && active) ? __uint_as_float(sv[i]) * a.scale_log2e : -CUDART_INF_F;
+        for (int i = 0; i < kBsBlk / 2; ++i) {
+          const uint32_t hi = __shfl_sync(0xffffffffu, sv[kBsBlk / 2 + i], lane & 15);
+          const float x = __uint_as_float(active ? sv[i] : hi) * a.scale_log2e;
+          s[i] = listed ? x : -CUDART_INF_F;
           bmax = fmaxf(bmax, s[i]);
         }
+        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 16));
         const float m_new = fmaxf(m, bmax);
         const bool grow = m_new - m > 8.f;             // also true when m is still -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
@@ -299,7 +305,7 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             if (!ok) break;
             tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < kBsD; c += 32) {
+            for (int c = 0; c < kBsD; c += 32) {       // lanes 0-15 scale their rows; the shadow lanes' rows are unused
               uint32_t ov[32];
               tmem_ld32(t_row + kBsColO + c, ov);
               tmem_wait_ld();
@@ -311,24 +317,26 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           }
         }
         const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-        uint32_t pk[kBsBlk / 2];
+        uint32_t pk[kBsBlk / 4];
         float psum = 0.f;
 #pragma unroll
-        for (int i = 0; i < kBsBlk; i += 2) {
+        for (int i = 0; i < kBsBlk / 2; i += 2) {
           const float p0 = bs_exp2(s[i] - m_eff), p1 = bs_exp2(s[i + 1] - m_eff);
           psum += p0 + p1;
           pk[i >> 1] = bs_pack_bf16x2(p0, p1);
         }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 16);
         l += psum;
         if (jt > 0) {                                  // P is single-buffered: P.V of the previous block (of any unit) must be done
           ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(jt - 1) & 1], ((jt - 1) >> 1) & 1, abort_flag, a.status));
           if (!ok) break;
         }
-        if (active) {                                  // this row of P: 128 bytes, K-major, 128-byte swizzle
+        {                                              // this lane's half row of P: 64 bytes, K-major, 128-byte swizzle
           uint8_t* dst = p_s + row * 128;
+          const int c0 = (lane >> 4) * 4;              // first 16-byte chunk: columns 0-31 or 32-63
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(dst + (((c0 + c) ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         }
         fence_async_smem();                            // visible to the tensor core's reads
         tc_fence_before();
