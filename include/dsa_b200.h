@@ -126,7 +126,7 @@ int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_
  *   lut[b,h,s/64,0..num[b,h,s/64]) of query block s/64.
  *   q, k, v, out [B, S, H, 128] bf16, contiguous, 16-byte aligned; S a multiple of 64;
  *   lut [B, H, S/64, topk] int32 key-block ids (an id outside [0, S/64) contributes nothing and
- *   sets status 2); num [B, H, S/64] int32, clamped to [0, topk]. */
+ *   sets status 2); num [B, H, S/64] int32, clamped to [0, topk]; scale > 0. */
 int dsa_block_sparse_mha(const void* q_bf16, const void* k_bf16, const void* v_bf16, const int32_t* lut,
                          const int32_t* num, void* out_bf16, int B, int S, int H, int D, int topk, float scale,
                          int32_t* status, void* stream);

@@ -284,16 +284,20 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         // An M = 64 accumulator keeps its rows in lanes 0-15 of the quadrant, so lanes 16-31 would idle (and
         // pay for 64 exponentials of garbage).  Each row is split instead: lane r keeps columns 0-31, lane
         // r + 16 receives columns 32-63 by shuffle; maximum and sum are combined across the pair.
-        float s[kBsBlk / 2];
+        float x[kBsBlk / 2];                           // raw scores; the (positive) scale is folded into the exponent's FMA
         float bmax = -CUDART_INF_F;
 #pragma unroll
         for (int i = 0; i < kBsBlk / 2; ++i) {
           const uint32_t hi = __shfl_sync(0xffffffffu, sv[kBsBlk / 2 + i], lane & 15);
-          const float x = __uint_as_float(active ? sv[i] : hi) * a.scale_log2e;
-          s[i] = listed ? x : -CUDART_INF_F;
-          bmax = fmaxf(bmax, s[i]);
+          x[i] = __uint_as_float(active ? sv[i] : hi);
+          bmax = fmaxf(bmax, x[i]);
         }
-        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 16));
+        if (!listed) {                                 // a bad list entry (uniform, rare): the whole block is masked
+#pragma unroll
+          for (int i = 0; i < kBsBlk / 2; ++i) x[i] = -CUDART_INF_F;
+          bmax = -CUDART_INF_F;
+        }
+        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 16)) * a.scale_log2e;
         const float m_new = fmaxf(m, bmax);
         const bool grow = m_new - m > 8.f;             // also true when m is still -inf and m_new is finite
         if (__any_sync(0xffffffffu, grow)) {
@@ -321,7 +325,7 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         float psum = 0.f;
 #pragma unroll
         for (int i = 0; i < kBsBlk / 2; i += 2) {
-          const float p0 = bs_exp2(s[i] - m_eff), p1 = bs_exp2(s[i + 1] - m_eff);
+          const float p0 = bs_exp2(fmaf(x[i], a.scale_log2e, -m_eff)), p1 = bs_exp2(fmaf(x[i + 1], a.scale_log2e, -m_eff));
           psum += p0 + p1;
           pk[i >> 1] = bs_pack_bf16x2(p0, p1);
         }

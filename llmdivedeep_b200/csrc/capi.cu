@@ -153,6 +153,7 @@ int dsa_block_sparse_mha(const void* q_bf16, const void* k_bf16, const void* v_b
   g_err[0] = 0;
   if (B < 0 || S < 0 || H < 0 || topk < 0) return set_error(DSA_ERR_SHAPE, "block_sparse_mha: negative size");
   if (D != 128) return set_error(DSA_ERR_SHAPE, "block_sparse_mha: head dim %d, only 128 is built", D);
+  if (!(scale > 0.f)) return set_error(DSA_ERR_ARG, "block_sparse_mha: the softmax scale must be positive");
   if (S % 64) return set_error(DSA_ERR_SHAPE, "block_sparse_mha: S (%d) must be a multiple of the 64-token block", S);
   if (B == 0 || S == 0 || H == 0) return DSA_OK;
   if (!q_bf16 || !k_bf16 || !v_bf16 || !out_bf16 || !num || (topk > 0 && !lut))
