@@ -114,7 +114,7 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_fp8, const float* k_scale,
  * sparse-MLA kernel of its own.
  *   q_bf16 [T, H, 576] bf16; kv_bf16 [S_kv, 576] bf16; idx [T, K] int32 positions
  *   into kv (negative = empty; >= S_kv is skipped and sets status 2);
- *   out_bf16 [T, H, 512] bf16.  All contiguous and 16-byte aligned.  K <= 2048.  Any H >= 1
+ *   out_bf16 [T, H, 512] bf16.  All contiguous and 16-byte aligned.  K <= 2048; scale > 0.  Any H >= 1
  *   (heads are processed in groups of 128). */
 int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_t* idx, void* out_bf16, int T, int H,
                            int S_kv, int K, float scale, int32_t* status, void* stream);

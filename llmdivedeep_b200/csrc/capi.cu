@@ -143,6 +143,7 @@ int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_
   if ((int64_t)T * H > 0x7fffffffLL || T > 0x7fffffff / 2) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: T*H too large");
   if (H > 128 * 65535) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: too many heads");
   if (K > 2048) return set_error(DSA_ERR_SHAPE, "sparse_mla_prefill: K (%d) exceeds 2048 selected keys per query", K);
+  if (!(scale > 0.f)) return set_error(DSA_ERR_ARG, "sparse_mla_prefill: the softmax scale must be positive");
   return sparse_mla_prefill_launch(q_bf16, kv_bf16, idx, out_bf16, T, H, S_kv, K, scale, status,
                                    static_cast<cudaStream_t>(stream));
 }
@@ -181,6 +182,7 @@ int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int
   if (table_stride * 64 < max_ctx)
     return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: block table row shorter than max_ctx");
   if (K > 2048) return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: K (%d) exceeds 2048 selected keys per query", K);
+  if (!(scale > 0.f)) return set_error(DSA_ERR_ARG, "sparse_mla_decode_paged: the softmax scale must be positive");
   if ((int64_t)num_pages * 64 > 0x7fffffffLL || (int64_t)B * H > 0x7fffffffLL)
     return set_error(DSA_ERR_SHAPE, "sparse_mla_decode_paged: problem too large");
   if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15))

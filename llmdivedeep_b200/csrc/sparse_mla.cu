@@ -382,15 +382,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(s_free);                             // the next block's scores may overwrite S now
-      float s[kMlaBlk];
+      float s[kMlaBlk];                                // raw scores; the (positive) scale is folded into the exponent's FMA
       float bmax = -CUDART_INF_F;
       const int* vrow = rows_all + j * kMlaBlk;
 #pragma unroll
       for (int i = 0; i < kMlaBlk; ++i) {
-        const float x = __uint_as_float(sv[i]) * a.scale_log2e;
-        s[i] = vrow[i] >= 0 ? x : -CUDART_INF_F;
+        s[i] = vrow[i] >= 0 ? __uint_as_float(sv[i]) : -CUDART_INF_F;
         bmax = fmaxf(bmax, s[i]);
       }
+      bmax *= a.scale_log2e;
       const float m_new = fmaxf(m, bmax);
       const bool grow = m_new - m > 8.f;               // also true when m is still -inf and m_new is finite
       if (__any_sync(0xffffffffu, grow)) {
@@ -418,7 +418,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
       float psum = 0.f;
 #pragma unroll
       for (int i = 0; i < kMlaBlk; i += 2) {
-        const float p0 = fast_exp2(s[i] - m_eff), p1 = fast_exp2(s[i + 1] - m_eff);
+        const float p0 = fast_exp2(fmaf(s[i], a.scale_log2e, -m_eff)), p1 = fast_exp2(fmaf(s[i + 1], a.scale_log2e, -m_eff));
         psum += p0 + p1;
         pk[i >> 1] = pack_bf16x2(p0, p1);
       }
