@@ -35,10 +35,10 @@ constexpr int kBsTileBytes = 2 * kBsPanelBytes;    // [64 rows x 128 dims]
 constexpr int kBsKStages = 3;                      // K tiles in flight: a K stage is free once its scores are computed
 constexpr int kBsVStages = 2;                      // V tiles in flight: needed one softmax later, freed after P.V
 constexpr int kBsThreads = 256;
-constexpr int kBsSmemBytes = 1024 + kBsTileBytes /*Q*/ + (kBsKStages + kBsVStages) * kBsTileBytes /*K,V*/ +
-                             kBsPanelBytes /*P*/ + 256 /*barriers*/;
-static_assert(2 * kBsSmemBytes <= 227 * 1024, "two CTAs per SM");
-constexpr uint32_t kBsColO = 0, kBsColS = 128, kBsTmemCols = 256;
+constexpr int kBsSmemBytes = kBsTileBytes /*Q*/ + (kBsKStages + kBsVStages) * kBsTileBytes /*K,V*/ +
+                             2 * kBsPanelBytes /*P, double-buffered*/ + 256 /*barriers*/;
+static_assert(2 * (kBsSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM (1 KB per CTA is reserved by the system)");
+constexpr uint32_t kBsColO = 0, kBsColS = 128 /* two score buffers of 64 columns */, kBsTmemCols = 256;
 
 struct BsArgs {
   const int32_t* lut;          // [B, H, nqb, topk]
@@ -63,26 +63,25 @@ __device__ __forceinline__ float bs_exp2(float x) {
 __global__ void __launch_bounds__(kBsThreads, 2)
 block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_v, const BsArgs a, const int n_units) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];           // the swizzled tiles need 1024-byte alignment
   uint8_t* q_s = smem;                                        // 2 panels [64 rows x 128 B]
   uint8_t* k_s = q_s + kBsTileBytes;                          // stages x 2 panels
   uint8_t* v_s = k_s + kBsKStages * kBsTileBytes;             // stages x 2 panels
-  uint8_t* p_s = v_s + kBsVStages * kBsTileBytes;             // [64 rows x 64 keys] bf16, one panel
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kBsPanelBytes);
+  uint8_t* p_s = v_s + kBsVStages * kBsTileBytes;             // 2 x [64 rows x 64 keys] bf16, one panel each
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * kBsPanelBytes);
   uint64_t* q_full = bars + 0;                                // TMA -> MMA, once per unit
   uint64_t* q_empty = bars + 1;                               // the unit's last scores are issued: Q may be replaced
   uint64_t* k_full = bars + 2;                                // [3] TMA -> MMA
   uint64_t* k_free = bars + 5;                                // [3] the scores of the block are computed
   uint64_t* v_full = bars + 8;                                // [2] TMA -> MMA
   uint64_t* v_free = bars + 10;                               // [2] P.V of the block finished
-  uint64_t* s_full = bars + 12;                               // MMA -> softmax
-  uint64_t* s_free = bars + 13;                               // softmax has read S
-  uint64_t* p_full = bars + 14;                               // softmax -> MMA
-  uint64_t* pv_done = bars + 15;                              // [2] P.V of a block finished: O quiescent, P free
-  uint64_t* o_final = bars + 17;                              // the unit's last P.V finished
-  uint64_t* o_free = bars + 18;                               // the unit's O has been read out
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  uint64_t* s_full = bars + 12;                               // [2] MMA -> softmax
+  uint64_t* s_free = bars + 14;                               // [2] softmax has read that score buffer
+  uint64_t* p_full = bars + 16;                               // [2] softmax -> MMA
+  uint64_t* pv_done = bars + 18;                              // [2] P.V of a block finished: O quiescent, that P buffer free
+  uint64_t* o_final = bars + 20;                              // the unit's last P.V finished
+  uint64_t* o_free = bars + 21;                               // the unit's O has been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -102,15 +101,19 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       mbar_init(&v_full[i], 1);
       mbar_init(&v_free[i], 1);
       mbar_init(&pv_done[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 128);
+      mbar_init(&p_full[i], 128);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 128);
-    mbar_init(p_full, 128);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
+  }
+  if (smem_u32(smem) & 1023u) {                               // never seen; the tiles would be mis-swizzled: refuse, do not compute
+    if (threadIdx.x == 0 && a.status) atomicCAS(a.status, kStatusOk, kStatusWaitTimeout);
+    return;
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kBsTmemCols);
@@ -197,53 +200,70 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const uint64_t kdesc0 = umma_smem_desc(smem_u32(k_s), 16, 1024, kSwz128);
       const uint64_t vdesc0 = umma_smem_desc(smem_u32(v_s), kBsPanelBytes, 1024, kSwz128);
       constexpr uint64_t kStage = kBsTileBytes >> 4, kPanel = kBsPanelBytes >> 4;
-      uint32_t nq = 0, jt = 0;                                // jt: blocks whose scores have been issued... of finished units
+      uint32_t nq = 0, jt = 0;                                // jt: running index of the unit's first block
       bool ok = true;
-      auto issue_qk = [&](uint32_t t) -> bool {               // scores of running block t
+      // Scores run up to two blocks ahead of the softmax (two score buffers in tensor memory): block t is issued
+      // as soon as its K tile has landed and the softmax has read block t-2 out of the same buffer.
+      auto qk_ready = [&](uint32_t t) -> bool {
+        return mbar_try_wait(&k_full[t % kBsKStages], (t / kBsKStages) & 1) &&
+               (t < 2 || mbar_try_wait(&s_free[t & 1], ((t >> 1) - 1) & 1));
+      };
+      auto issue_qk = [&](uint32_t t) {                       // both waits have succeeded
         const int st = t % kBsKStages;
-        if (!mbar_wait(&k_full[st], (t / kBsKStages) & 1, abort_flag, a.status)) return false;
-        if (t > 0 && !mbar_wait(s_free, (t - 1) & 1, abort_flag, a.status)) return false;
         tc_fence_after();
 #pragma unroll
         for (int p = 0; p < 2; ++p)
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma_f16_ss(tmem + kBsColS, qdesc + p * kPanel + 2 * ks, kdesc0 + st * kStage + p * kPanel + 2 * ks, idesc_qk,
-                        (p | ks) != 0);
-        umma_commit(s_full);
+            umma_f16_ss(tmem + kBsColS + (t & 1) * kBsBlk, qdesc + p * kPanel + 2 * ks,
+                        kdesc0 + st * kStage + p * kPanel + 2 * ks, idesc_qk, (p | ks) != 0);
+        umma_commit(&s_full[t & 1]);
         umma_commit(&k_free[st]);
-        return true;
       };
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
         const int n = unit_len(u);
         if (n == 0) continue;
         ok = mbar_wait(q_full, nq & 1, abort_flag, a.status);
-        if (ok) ok = issue_qk(jt);
-        if (ok && n == 1) umma_commit(q_empty);
         if (ok && nq > 0) ok = mbar_wait(o_free, (nq - 1) & 1, abort_flag, a.status);   // the previous unit's O is read out
+        uint32_t qk_next = jt;                                // next block whose scores are to be issued
+        const uint32_t unit_end = jt + n;
         for (int j = 0; j < n && ok; ++j) {
           const uint32_t t = jt + j;
           const int st = t & 1;
-          bool qk_done = j + 1 >= n;
-          if (!qk_done && mbar_try_wait(&k_full[(t + 1) % kBsKStages], ((t + 1) / kBsKStages) & 1)) {   // next scores while this softmax runs
-            ok = issue_qk(t + 1);
-            if (ok && j + 2 == n) umma_commit(q_empty);       // those were the unit's last scores
-            qk_done = true;
+          // issue scores ahead while waiting for this block's P (and V): never stall P.V behind a late K tile,
+          // never leave the tensor pipe idle while one is there
+          bool have_p = false;
+          for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+            if (qk_next < unit_end && qk_next <= t + 2 && qk_ready(qk_next)) {
+              issue_qk(qk_next);
+              if (++qk_next == unit_end) umma_commit(q_empty);   // those were the unit's last scores: Q may be replaced
+              continue;
+            }
+            if (qk_next > t && mbar_try_wait(&v_full[st], (t >> 1) & 1) && mbar_try_wait(&p_full[t & 1], (t >> 1) & 1)) {
+              have_p = true;
+              break;
+            }
+            if (spin > kFastSpins) {
+              if (*abort_flag) break;
+              __nanosleep(40);
+            }
           }
-          if (!ok) break;
-          ok = mbar_wait(&v_full[st], (t >> 1) & 1, abort_flag, a.status) && mbar_wait(p_full, t & 1, abort_flag, a.status);
-          if (!ok) break;
+          if (!have_p) {
+            if (!*abort_flag) {
+              *abort_flag = 1;
+              if (a.status) atomicCAS(a.status, kStatusOk, kStatusWaitTimeout);
+            }
+            ok = false;
+            break;
+          }
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < kBsBlk / 16; ++ks)    // 16 keys per step: 32 B along P's rows, 16 rows x 128 B into each V panel
-            umma_f16_ss(tmem + kBsColO, pdesc + 2 * ks, vdesc0 + st * kStage + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
+            umma_f16_ss(tmem + kBsColO, pdesc + (t & 1) * kPanel + 2 * ks, vdesc0 + st * kStage + ks * (2048 >> 4), idesc_pv,
+                        (j | ks) != 0);
           umma_commit(&v_free[st]);
           umma_commit(&pv_done[t & 1]);
           if (j == n - 1) umma_commit(o_final);
-          if (!qk_done) {
-            ok = issue_qk(t + 1);
-            if (ok && j + 2 == n) umma_commit(q_empty);
-          }
         }
         jt += n;
         ++nq;
@@ -271,15 +291,15 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       float m = -CUDART_INF_F, l = 0.f;
       for (int j = 0; j < n && ok; ++j, ++jt) {
         const int kb = __ldg(list + j);                       // requested before the wait: only its validity is needed
-        ok = __all_sync(0xffffffffu, mbar_wait(s_full, jt & 1, abort_flag, a.status));
+        ok = __all_sync(0xffffffffu, mbar_wait(&s_full[jt & 1], (jt >> 1) & 1, abort_flag, a.status));
         if (!ok) break;
         tc_fence_after();
         uint32_t sv[kBsBlk];
-        tmem_ld32(t_row + kBsColS, *reinterpret_cast<uint32_t(*)[32]>(sv));
-        tmem_ld32(t_row + kBsColS + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
+        tmem_ld32(t_row + kBsColS + (jt & 1) * kBsBlk, *reinterpret_cast<uint32_t(*)[32]>(sv));
+        tmem_ld32(t_row + kBsColS + (jt & 1) * kBsBlk + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(s_free);
+        mbar_arrive(&s_free[jt & 1]);
         const bool listed = kb >= 0 && kb < nkb;
         // An M = 64 accumulator keeps its rows in lanes 0-15 of the quadrant, so lanes 16-31 would idle (and
         // pay for 64 exponentials of garbage).  Each row is split instead: lane r keeps columns 0-31, lane
@@ -331,12 +351,12 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         }
         psum += __shfl_xor_sync(0xffffffffu, psum, 16);
         l += psum;
-        if (jt > 0) {                                  // P is single-buffered: P.V of the previous block (of any unit) must be done
-          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(jt - 1) & 1], ((jt - 1) >> 1) & 1, abort_flag, a.status));
+        if (jt > 1) {                                  // two P buffers: P.V of block jt-2 (of any unit) read this one
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[jt & 1], ((jt >> 1) - 1) & 1, abort_flag, a.status));
           if (!ok) break;
         }
         {                                              // this lane's half row of P: 64 bytes, K-major, 128-byte swizzle
-          uint8_t* dst = p_s + row * 128;
+          uint8_t* dst = p_s + (jt & 1) * kBsPanelBytes + row * 128;
           const int c0 = (lane >> 4) * 4;              // first 16-byte chunk: columns 0-31 or 32-63
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -344,7 +364,7 @@ block_sparse_mha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         }
         fence_async_smem();                            // visible to the tensor core's reads
         tc_fence_before();
-        mbar_arrive(p_full);
+        mbar_arrive(&p_full[jt & 1]);
       }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, nq & 1, abort_flag, a.status));
       if (!ok) break;
