@@ -13,11 +13,15 @@
 //     V [64 x 128], each as two 128-byte-swizzled panels of 64 dims, into a 3-stage K ring and a 2-stage V ring;
 //     32 list entries are read at a time, one per lane.
 //   * warp 1: owns the tensor memory; lane 0 issues S = Q K^T (8 tcgen05.mma kind::f16, K-major
-//     operands) and O += P V (4 MMAs; P from shared memory, V read through an MN-major descriptor, so
-//     the [key][dim] tile needs no transpose).
-//   * warps 4-7: online softmax, thread = query row.  Scores come from tensor memory, P goes to shared
-//     memory as bf16 in the K-major swizzled layout; the running maximum is raised (and O rescaled in
-//     tensor memory) only when it grows by more than 8 in log2 units.
+//     operands) into one of two score buffers, up to two blocks ahead of the softmax, and O += P V
+//     (4 MMAs; P from shared memory, V read through an MN-major descriptor, so the [key][dim] tile needs
+//     no transpose).  It polls "next K landed and its score buffer read" and "this block's P and V
+//     ready" together, so neither a late K tile nor a slow softmax leaves the tensor pipe idle.
+//   * warps 4-7: online softmax.  Scores come from tensor memory; a row (lanes 0-15 of the quadrant) is
+//     split over a lane pair -- lane r keeps columns 0-31, lane r+16 receives 32-63 by shuffle -- so all
+//     32 lanes compute; P goes to one of two shared-memory buffers as bf16 in the K-major swizzled
+//     layout; the running maximum is raised (and O rescaled in tensor memory) only when it grows by
+//     more than 8 in log2 units.
 // Every wait is bounded (dsa_common.cuh).
 #include <cuda.h>
 #include <cudaTypedefs.h>
