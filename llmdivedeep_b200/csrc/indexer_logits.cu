@@ -549,10 +549,8 @@ struct RwCfg {
   static constexpr int K_TILE_BYTES = kTileKeys * D, Q_TILE_BYTES = N * D;
   static constexpr int STAGES = 6;
   static constexpr int EPI_WG = 4, EPI_WARPS = 16, THREADS = 128 + EPI_WG * 128;
-  static constexpr int AHEAD = 2;
   static constexpr uint32_t SBO = 8 * D;
-  static constexpr int SMEM_BYTES = 1024 + STAGES * K_TILE_BYTES + 2 * Q_TILE_BYTES + 2 * N * 4 + 2 * NQ * 8 + 256 +
-                                    AHEAD * EPI_WG * 128 * 4;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * K_TILE_BYTES + 2 * Q_TILE_BYTES + 2 * N * 4 + 2 * NQ * 8 + 256;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -577,7 +575,6 @@ indexer_logits_rw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   uint64_t* w_empty = w_full + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* ks_ring = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // AHEAD x epilogue threads
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -714,7 +711,6 @@ indexer_logits_rw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const int wq = warp & 3;                     // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;              // key within the tile = TMEM lane
     const uint32_t t_lane = tmem_base + (uint32_t(wq * 32) << 16) + tok * C::H;
-    float* my_ring = ks_ring + (threadIdx.x - 128);
     uint32_t it = 0, nu = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
@@ -738,20 +734,12 @@ indexer_logits_rw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       if (lane == 0) mbar_arrive(&w_empty[ub]);  // weights and window are in registers
       const int t_tok = g * C::NQ + tok;
       float* out_row = a.logits + (int64_t)t_tok * a.ld;
-      auto prefetch_kscale = [&](int tile) {
-        if (tile < t_hi) {
-          const int sk = tile * kTileKeys + row;
-          cp_async_f32(my_ring + (tile % C::AHEAD) * (C::EPI_WG * 128), a.k_scale + (sk < a.S ? sk : 0), sk < a.S);
-        }
-        cp_async_commit();
-      };
-#pragma unroll
-      for (int i = 0; i < C::AHEAD; ++i) prefetch_kscale(t_lo + i);
       for (int kt = t_lo; kt < t_hi && ok; ++kt, ++it) {
         const int stage = it & 1;
-        cp_async_wait<C::AHEAD - 1>();
-        const float kscale = my_ring[(kt % C::AHEAD) * (C::EPI_WG * 128)];
-        prefetch_kscale(kt + C::AHEAD);
+        // k_scale is only needed for the last multiply of the tile: a plain load requested here has the whole
+        // tile's work to arrive (the array is L2-resident), and nothing is carried from tile to tile
+        const int s = kt * kTileKeys + row;              // key position
+        const float kscale = s < a.S ? __ldg(a.k_scale + s) : 0.f;
         ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[stage], (it >> 1) & 1, abort_flag, a.status));
         if (!ok) break;
         tc_fence_after();
@@ -780,13 +768,11 @@ indexer_logits_rw_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         unpack_f32x2(chain[0], e0, o0);
         unpack_f32x2(chain[1], e1, o1);
         const float score = (0.f + (e0 + o0)) + (e1 + o1);
-        const int s = kt * kTileKeys + row;              // key position
         if (s < a.S && t_tok < a.T) {
           const bool in = static_cast<uint32_t>(s - win.x) < static_cast<uint32_t>(win.y);
           out_row[s] = in ? score * kscale : -CUDART_INF_F;
         }
       }
-      cp_async_wait<0>();
       ++nu;
     }
   }
