@@ -500,8 +500,8 @@ def main():
     achieved = flops / (k_ms * 1e-3) / 1e12
     peak_fp8 = 2.0 * peaks["bf16_tflops"]
     # dram__bytes_read + dram__bytes_write of the indexer kernel from one ncu capture of the 512-row reduced
-    # case (13.32 MB read + 76.51 MB written), scaled by the row count (traffic is proportional to query rows)
-    traffic = (13.32e6 + 76.51e6) * T_ROWS / 512
+    # case (13.44 MB read + 76.45 MB written), scaled by the row count (traffic is proportional to query rows)
+    traffic = (13.44e6 + 76.45e6) * T_ROWS / 512
     topk_bytes = 4.0 * causal_keys + T_ROWS * TOPK * 4
 
     line = {
