@@ -158,16 +158,42 @@ int dsa_sparse_mla_decode_paged(const void* q_bf16, const void* cache, const int
  * library keeps until the process exits.  Limits and rules:
  *   - min(T, 256) * round_up(S, 4) * 4 bytes must fit in 64 MiB (S <= 65536 when
  *     T >= 256); larger problems are refused with DSA_ERR_WORKSPACE.
- *   - The first call on each device looks up the array's device address; make
- *     that first call outside any stream capture.
+ *   - The first call on each device looks up the array's device address, and
+ *     that lookup is when the driver materialises the 64 MiB on that device (CUDA
+ *     loads modules lazily): it can fail with DSA_ERR_CUDA "out of memory" on a
+ *     GPU that is already full.  Make one warm-up call with T = 0 per device at
+ *     start-up -- before the host freezes its pool and outside any stream
+ *     capture; it launches nothing.
  *   - All calls on one device share the array, which keeps whatever the last
  *     call left there (every call overwrites what it reads).  Two calls whose
  *     kernels overlap on the GPU (different streams) race: serialise them.
- *   - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine; after
+ *     the warm-up call no device memory changes hands at all. */
 size_t dsa_indexer_topk_static_max_bytes(void);
 int dsa_indexer_topk_static(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
                             const int32_t* ks, const int32_t* ke, int T, int S, int H, int D, int k,
                             int32_t* out_idx, int32_t* status, void* stream);
+
+/* ---- test hooks ---------------------------------------------------------------
+ * No counterpart in the reference.  They exist so that the parity tests can reach,
+ * through this ABI, code paths that the normal entry points choose by themselves.
+ *
+ * dsa_test_indexer_logits_general: dsa_indexer_logits with 64 heads x 128 kept on
+ *   the general kernel (the normal call takes the register-weight kernel for that
+ *   shape); the two must agree bit for bit.
+ * dsa_test_topk_select_two_pass: dsa_topk_select with every row on the two-pass
+ *   radix path (the normal call takes the sampled single pass for long rows and
+ *   falls back to this path when the sample misleads it); same sets, same order.
+ * dsa_test_bounded_wait: launches one thread that waits, with the wait helper all
+ *   pipeline roles use, on a barrier nobody arrives at; after poll_limit
+ *   (1..65536) polls it must give up and write status 1 to *status. */
+int dsa_test_indexer_logits_general(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w,
+                                    int w_dtype, const int32_t* ks, const int32_t* ke, float* logits,
+                                    int64_t ld_logits, int T, int S, int H, int D, int clean, int32_t* status,
+                                    void* stream);
+int dsa_test_topk_select_two_pass(const float* logits, int64_t ld_logits, const int32_t* ks, const int32_t* ke, int T,
+                                  int S, int k, int32_t* out_idx, void* stream);
+int dsa_test_bounded_wait(int poll_limit, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -191,7 +191,8 @@ def _rope_cossin(S: int, dim: int, device, base: float = 10000.0):
 
 def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleave: bool) -> torch.Tensor:
     """RoPE on the whole last dim of x: NeoX halves or GPT-J even/odd pairs (DSA.py:444-469).
-    Like the reference, the NeoX form returns the fp32 products unrounded (bf16 x fp32 promotes),
+    Like the reference, the NeoX form returns the fp32 products unrounded (bf16 x times the fp32 table
+    promotes, so q and k reach the quantiser as fp32 with the un-rotated dims holding bf16 values);
     the interleaved form rounds back to x's dtype (the reference writes into ``empty_like(x)``)."""
     if x.dim() == 3:
         cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
@@ -200,7 +201,7 @@ def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleave: b
         return torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).flatten(-2).to(x.dtype)
     h = x.shape[-1] // 2
     a, b = x[..., :h], x[..., h:]
-    return torch.cat((a * cos - b * sin, a * sin + b * cos), dim=-1).to(x.dtype)
+    return torch.cat((a * cos - b * sin, a * sin + b * cos), dim=-1)      # fp32 for bf16 x: no rounding here
 
 
 def _rope_head(x: torch.Tensor, rd: int, S: int, interleave: bool) -> torch.Tensor:

@@ -37,6 +37,12 @@ SIGNATURES = {
     "dsa_sparse_mla_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "dsa_sparse_mla_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "dsa_test_indexer_logits_general": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                c_void_p]),
+    "dsa_test_topk_select_two_pass": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                              c_void_p]),
+    "dsa_test_bounded_wait": (c_int, [c_int, c_void_p, c_void_p]),
     "dsa_indexer_topk_static_max_bytes": (c_size_t, []),
     "dsa_indexer_topk_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -41,13 +41,14 @@ int sm_count() {
 // launchers implemented next to their kernels
 int indexer_logits_contiguous(const void* q, const void* k, const float* k_scale, const void* w, int w_dtype,
                               const int32_t* ks, const int32_t* ke, float* logits, int64_t ld, int T, int S,
-                              int H, int D, int clean, int32_t* status, cudaStream_t stream);
+                              int H, int D, int clean, int general, int32_t* status, cudaStream_t stream);
 int indexer_logits_paged(const void* q, const void* w, int w_dtype, const void* kcache, const float* kscale,
                          const int32_t* block_table, int64_t table_stride, const int32_t* ctx_len, float* logits,
                          int64_t ld, int B, int H, int D, int num_pages, int max_ctx, int32_t* status,
                          cudaStream_t stream);
 int topk_select_launch(const float* logits, int64_t ld, const int32_t* ks, const int32_t* ke, int T, int S, int k,
-                       int32_t* out, cudaStream_t stream);
+                       int32_t* out, int sample, cudaStream_t stream);
+int bounded_wait_probe_launch(uint32_t poll_limit, int32_t* status, cudaStream_t stream);
 
 int sparse_mla_prefill_launch(const void* q, const void* kv, const int32_t* idx, void* out, int T, int H, int S_kv,
                               int K, float scale, int32_t* status, cudaStream_t stream);
@@ -69,15 +70,9 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 using namespace dsa;
 
-extern "C" {
-
-int dsa_version(void) { return 100; }
-
-const char* dsa_last_error_string(void) { return g_err; }
-
-int dsa_indexer_logits(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
-                       const int32_t* ks, const int32_t* ke, float* logits, int64_t ld_logits, int T, int S,
-                       int H, int D, int clean, int32_t* status, void* stream) {
+static int indexer_logits_checked(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
+                                  const int32_t* ks, const int32_t* ke, float* logits, int64_t ld_logits, int T, int S,
+                                  int H, int D, int clean, int general, int32_t* status, void* stream) {
   g_err[0] = 0;
   if (T < 0 || S < 0) return set_error(DSA_ERR_SHAPE, "indexer_logits: negative size (T=%d, S=%d)", T, S);
   if (T == 0 || S == 0) return DSA_OK;
@@ -93,7 +88,53 @@ int dsa_indexer_logits(const void* q_fp8, const void* k_fp8, const float* k_scal
     return set_error(DSA_ERR_SHAPE, "indexer_logits: ld_logits (%lld) too large (64 * ld must stay below 2^31)",
                      (long long)ld_logits);
   return indexer_logits_contiguous(q_fp8, k_fp8, k_scale, w, w_dtype, ks, ke, logits, ld_logits, T, S, H, D, clean,
-                                   status, static_cast<cudaStream_t>(stream));
+                                   general, status, static_cast<cudaStream_t>(stream));
+}
+
+static int topk_select_checked(const float* logits, int64_t ld_logits, const int32_t* ks, const int32_t* ke, int T, int S,
+                               int k, int32_t* out_idx, int sample, void* stream) {
+  g_err[0] = 0;
+  if (T < 0 || S < 0 || k < 0) return set_error(DSA_ERR_SHAPE, "topk_select: negative size");
+  if (T == 0 || k == 0) return DSA_OK;
+  if (!logits || !out_idx) return set_error(DSA_ERR_ARG, "topk_select: NULL pointer argument");
+  if (ld_logits < S) return set_error(DSA_ERR_SHAPE, "topk_select: ld_logits < S");
+  if (k > 65535) return set_error(DSA_ERR_SHAPE, "topk_select: k (%d) exceeds 65535", k);
+  return topk_select_launch(logits, ld_logits, ks, ke, T, S, k, out_idx, sample, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" {
+
+int dsa_version(void) { return 100; }
+
+const char* dsa_last_error_string(void) { return g_err; }
+
+int dsa_indexer_logits(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w, int w_dtype,
+                       const int32_t* ks, const int32_t* ke, float* logits, int64_t ld_logits, int T, int S,
+                       int H, int D, int clean, int32_t* status, void* stream) {
+  return indexer_logits_checked(q_fp8, k_fp8, k_scale, w, w_dtype, ks, ke, logits, ld_logits, T, S, H, D, clean,
+                                /*general=*/0, status, stream);
+}
+
+/* Test hooks (declared in include/dsa_b200.h under "test hooks"): the same calls pinned to the code path that the
+ * normal entry points only take for some shapes or rows, so that tests can compare the two. */
+int dsa_test_indexer_logits_general(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w,
+                                    int w_dtype, const int32_t* ks, const int32_t* ke, float* logits,
+                                    int64_t ld_logits, int T, int S, int H, int D, int clean, int32_t* status,
+                                    void* stream) {
+  return indexer_logits_checked(q_fp8, k_fp8, k_scale, w, w_dtype, ks, ke, logits, ld_logits, T, S, H, D, clean,
+                                /*general=*/1, status, stream);
+}
+
+int dsa_test_topk_select_two_pass(const float* logits, int64_t ld_logits, const int32_t* ks, const int32_t* ke, int T,
+                                  int S, int k, int32_t* out_idx, void* stream) {
+  return topk_select_checked(logits, ld_logits, ks, ke, T, S, k, out_idx, /*sample=*/0, stream);
+}
+
+int dsa_test_bounded_wait(int poll_limit, int32_t* status, void* stream) {
+  g_err[0] = 0;
+  if (poll_limit < 1 || poll_limit > (1 << 16)) return set_error(DSA_ERR_ARG, "test_bounded_wait: poll_limit must be in [1, 65536]");
+  if (!status) return set_error(DSA_ERR_ARG, "test_bounded_wait: NULL status");
+  return bounded_wait_probe_launch((uint32_t)poll_limit, status, static_cast<cudaStream_t>(stream));
 }
 
 int dsa_indexer_logits_paged(const void* q_fp8, const void* w, int w_dtype, const void* kcache,
@@ -122,13 +163,7 @@ int dsa_indexer_logits_paged(const void* q_fp8, const void* w, int w_dtype, cons
 
 int dsa_topk_select(const float* logits, int64_t ld_logits, const int32_t* ks, const int32_t* ke, int T, int S,
                     int k, int32_t* out_idx, void* stream) {
-  g_err[0] = 0;
-  if (T < 0 || S < 0 || k < 0) return set_error(DSA_ERR_SHAPE, "topk_select: negative size");
-  if (T == 0 || k == 0) return DSA_OK;
-  if (!logits || !out_idx) return set_error(DSA_ERR_ARG, "topk_select: NULL pointer argument");
-  if (ld_logits < S) return set_error(DSA_ERR_SHAPE, "topk_select: ld_logits < S");
-  if (k > 65535) return set_error(DSA_ERR_SHAPE, "topk_select: k (%d) exceeds 65535", k);
-  return topk_select_launch(logits, ld_logits, ks, ke, T, S, k, out_idx, static_cast<cudaStream_t>(stream));
+  return topk_select_checked(logits, ld_logits, ks, ke, T, S, k, out_idx, /*sample=*/1, stream);
 }
 
 int dsa_sparse_mla_prefill(const void* q_bf16, const void* kv_bf16, const int32_t* idx, void* out_bf16, int T, int H,

@@ -52,11 +52,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait for `parity` on `bar`.  Returns false (after flagging) when the wait
-// expired or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Wait for `parity` on `bar`, giving up after `limit` polls.  Returns false (after
+// flagging) when the wait expired or another role already aborted.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                int* status, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > kFastSpins) {
       if (*abort_flag) return false;
@@ -66,6 +66,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort_flag = 1;
   if (status) atomicCAS(status, kStatusOk, kStatusWaitTimeout);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, kSpinLimit);
 }
 
 // ---- TMA (tiled bulk tensor copies, global -> this CTA's shared memory) ----

@@ -888,18 +888,12 @@ static int launch_indexer_rw(const void* q, const void* k, const IndexerArgs& ar
   return check_launch("indexer_logits");
 }
 
-int indexer_logits_dispatch(const void* q, const void* k, const IndexerArgs& a, int H, int D, int clean,
+// general != 0 keeps 64 heads x 128 on the general kernel (the test hook that compares the two forms)
+int indexer_logits_dispatch(const void* q, const void* k, const IndexerArgs& a, int H, int D, int clean, int general,
                             cudaStream_t stream) {
-  static const bool epi4 = getenv("DSA_IDX_EPI4") != nullptr;
-  // DSA_IDX_RW=0 keeps 64 x 128 on the general kernel (used to compare the two forms)
-  const char* rw_env = getenv("DSA_IDX_RW");            // read per call: tests switch it to compare the two forms
-  const bool rw = !(rw_env && rw_env[0] == '0');
-  if (H == 64 && D == 128 && rw && !epi4) return launch_indexer_rw(q, k, a, clean, stream);
-#define DSA_IDX_CASE(h, d)                                                                \
-  if (H == h && D == d) {                                                                 \
-    if (epi4) return launch_indexer<h, d, 256 / h, false, 2, 4>(q, k, a, clean, stream);  \
-    return launch_indexer<h, d, 256 / h, false, 2, 2>(q, k, a, clean, stream);            \
-  }
+  if (H == 64 && D == 128 && !general) return launch_indexer_rw(q, k, a, clean, stream);
+#define DSA_IDX_CASE(h, d) \
+  if (H == h && D == d) return launch_indexer<h, d, 256 / h, false, 2, 2>(q, k, a, clean, stream);
   DSA_IDX_CASE(64, 128)
   DSA_IDX_CASE(32, 128)
   DSA_IDX_CASE(16, 128)
@@ -922,7 +916,7 @@ int indexer_logits_paged_dispatch(const void* q, const void* kcache, const Index
 
 int indexer_logits_contiguous(const void* q, const void* k, const float* k_scale, const void* w, int w_dtype,
                               const int32_t* ks, const int32_t* ke, float* logits, int64_t ld, int T, int S,
-                              int H, int D, int clean, int32_t* status, cudaStream_t stream) {
+                              int H, int D, int clean, int general, int32_t* status, cudaStream_t stream) {
   IndexerArgs a{};
   a.k_scale = k_scale;
   a.w = w;
@@ -937,7 +931,7 @@ int indexer_logits_contiguous(const void* q, const void* k, const float* k_scale
   a.num_phys_rows = S;
   a.w_is_bf16 = (w_dtype == DSA_W_BF16);
   a.status = status;
-  return indexer_logits_dispatch(q, k, a, H, D, clean, stream);
+  return indexer_logits_dispatch(q, k, a, H, D, clean, general, stream);
 }
 
 int indexer_logits_paged(const void* q, const void* w, int w_dtype, const void* kcache, const float* kscale,

@@ -6,6 +6,8 @@
 // an embedding whose allocator is not re-entrant.
 // For them the fp32 logits scratch of dsa_indexer_topk lives here, in a
 // file-scope device array that every GPU loading the library holds until exit.
+#include <mutex>
+
 #include "dsa_host.h"
 
 namespace dsa {
@@ -15,9 +17,14 @@ constexpr size_t kStaticScratchBytes = size_t(64) << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // The array's name is only a host-side handle; kernels need the device address,
-// looked up once per device with that device current.
+// looked up once per device with that device current.  Under CUDA's lazy module
+// loading this lookup is also the moment the driver creates the array's 64 MiB on
+// that device, so it can fail with "out of memory" on a GPU that is already full:
+// hosts make one T = 0 call per device at start-up, before they freeze their pool.
 static void* static_scratch_ptr() {
   static void* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     set_error(DSA_ERR_CUDA, "indexer_topk_static: cannot query the current device");
@@ -42,6 +49,7 @@ extern "C" size_t dsa_indexer_topk_static_max_bytes(void) { return dsa::kStaticS
 extern "C" int dsa_indexer_topk_static(const void* q_fp8, const void* k_fp8, const float* k_scale, const void* w,
                                        int w_dtype, const int32_t* ks, const int32_t* ke, int T, int S, int H, int D,
                                        int k, int32_t* out_idx, int32_t* status, void* stream) {
+  dsa::set_error(DSA_OK, "%s", "");      // a fresh call starts with an empty error string, like the other entry points
   if (T > 0 && S > 0) {
     // one chunk of min(T, 256) rows of the padded row length must fit
     const size_t ld = (size_t(S) + 3) & ~size_t(3);

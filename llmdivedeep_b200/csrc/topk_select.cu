@@ -582,12 +582,10 @@ topk_select_kernel(const float* __restrict__ logits, int64_t ld, const int32_t* 
   emit_candidates<kCandPerThread>(sm, ck, valid, prefix, need, n_above, k, o);
 }
 
+// sample = 0 forces the two-pass path on every row (the test hook that pits the two paths against each other)
 int topk_select_launch(const float* logits, int64_t ld, const int32_t* ks, const int32_t* ke, int T, int S, int k,
-                       int32_t* out, cudaStream_t stream) {
+                       int32_t* out, int sample, cudaStream_t stream) {
   if (T == 0 || k == 0) return DSA_OK;
-  // DSA_TOPK_NO_SAMPLE=1 forces the two-pass path on every row (used to test the two paths against each other)
-  const char* e = getenv("DSA_TOPK_NO_SAMPLE");
-  const int sample = (e && e[0] == '1') ? 0 : 1;
   topk_select_kernel<<<T, kTopkThreads, 0, stream>>>(logits, ld, ks, ke, T, S, k, out, sample);
   return check_launch("topk_select");
 }

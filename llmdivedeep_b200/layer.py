@@ -49,7 +49,8 @@ class DecodeWorkspace:
     def __init__(self, batch: int, heads: int, max_ctx: int, topk: int, device):
         ld = (max_ctx + 3) // 4 * 4
         self.logits = torch.empty(batch, ld, dtype=torch.float32, device=device)
-        self.idx = torch.empty(batch, topk, dtype=torch.int32, device=device)
+        self.k = min(topk, max_ctx)                    # selected keys per sequence (the kernels write rows at this stride)
+        self.idx = torch.empty(batch, self.k, dtype=torch.int32, device=device)
         self.out = torch.empty(batch, heads, 512, dtype=torch.bfloat16, device=device)
         need = _lib.load().dsa_sparse_mla_decode_workspace_bytes(batch, heads, min(topk, max_ctx))
         self.mla_ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
@@ -63,8 +64,7 @@ def dsa_decode_step(q_idx_fp8, w, kcache, kscale, block_table, ctx_len, q, laten
     context, sparse MLA over the paged FP8 latent cache.  Returns (idx, out) views of ``ws``."""
     B = q.shape[0]
     logits = ops.fp8_paged_mqa_logits(q_idx_fp8, w, kcache, kscale, block_table, ctx_len, ws.max_ctx, out=ws.logits)
-    k = min(ws.topk, ws.max_ctx)
-    ops.topk_select(logits, k, None, ctx_len, out=ws.idx[:B])
+    ops.topk_select(logits, ws.k, None, ctx_len, out=ws.idx[:B])
     ops.sparse_mla_decode_paged(q, latent_cache, block_table, ws.idx[:B], softmax_scale, ws.max_ctx, out=ws.out[:B],
                                 workspace=ws.mla_ws)
     return ws.idx[:B], ws.out[:B]

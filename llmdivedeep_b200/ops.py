@@ -25,15 +25,37 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
-def _need_cuda(*ts):
+def _need_cuda(*ts) -> torch.device:
+    """All tensors must live on ONE CUDA device; returns it.  The library launches on the current
+    device (tensor maps, SM count and the stream follow it), so every wrapper below makes this
+    device current around its call: a tensor of another GPU would otherwise be handed to a kernel
+    running on the wrong one."""
+    dev = None
     for t in ts:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise DsaError("libdsa_b200 kernels take CUDA tensors only (there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise DsaError(f"all tensors of one call must be on one device, got {dev} and {t.device}")
+    if dev is None:
+        raise DsaError("no tensor argument")
+    return dev
+
+
+def _dev_index(device) -> int:
+    d = torch.device(device)
+    if d.type != "cuda":
+        raise DsaError(f"not a CUDA device: {d}")
+    return torch.cuda.current_device() if d.index is None else d.index
 
 
 def status_word(device) -> torch.Tensor:
-    """The per-device int32 the kernels report soft errors into."""
-    key = torch.device(device).index or 0
+    """The per-device int32 the kernels report soft errors into (a device without an index means
+    the current one)."""
+    key = _dev_index(device)
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
     return _status[key]
@@ -65,12 +87,22 @@ def _as_i32(t: Optional[torch.Tensor], n: int, name: str) -> Optional[torch.Tens
     return t
 
 
+def _check_idx_out(out: Optional[torch.Tensor], T: int, k: int, device) -> torch.Tensor:
+    """The kernels write index rows at stride k: a caller-supplied ``out`` must be exactly that."""
+    if out is None:
+        return torch.empty(T, k, dtype=torch.int32, device=device)
+    if out.dtype != torch.int32 or tuple(out.shape) != (T, k) or not out.is_contiguous():
+        raise DsaError(f"out must be a contiguous int32 [{T}, {k}] tensor, got {out.dtype} {tuple(out.shape)} "
+                       f"strides {tuple(out.stride())}")
+    return out
+
+
 def fp8_mqa_logits(q_fp8, kv, weights, ks, ke, clean_logits: bool = True,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Drop-in for ``deep_gemm.fp8_mqa_logits(q_fp8, (k_fp8, k_scale), w, ks, ke)``
     as the reference calls it (sparse_attn/DSA.py:343-345).  Returns fp32 [T, S]."""
     k_fp8, k_scale = kv
-    _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke)
+    dev = _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke, out)
     if q_fp8.dtype != FP8 or k_fp8.dtype != FP8:
         raise DsaError("q and k must be float8_e4m3fn")
     if q_fp8.dim() != 3 or k_fp8.dim() != 2 or q_fp8.shape[2] != k_fp8.shape[1]:
@@ -92,9 +124,10 @@ def fp8_mqa_logits(q_fp8, kv, weights, ks, ke, clean_logits: bool = True,
     else:
         ld = out.stride(0)
     lib = _lib.load()
-    check(lib.dsa_indexer_logits(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
-                                 _ptr(ks), _ptr(ke), _ptr(out), ld, T, S, H, D, int(bool(clean_logits)),
-                                 _ptr(status_word(q_fp8.device)), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_indexer_logits(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
+                                     _ptr(ks), _ptr(ke), _ptr(out), ld, T, S, H, D, int(bool(clean_logits)),
+                                     _ptr(status_word(q_fp8.device)), _stream()))
     return out[:T, :S]
 
 
@@ -104,7 +137,7 @@ def fp8_paged_mqa_logits(q_fp8, weights, kcache, kscale, block_table, ctx_len, m
     kcache [num_pages*64,128] e4m3, kscale [num_pages*64] fp32, block_table [B,P] int32,
     ctx_len [B] int32.  Returns fp32 [B, max_ctx]; columns >= ctx_len[b] inside a
     processed 128-key tile hold -inf, columns beyond are uninitialised."""
-    _need_cuda(q_fp8, weights, kcache, kscale, block_table, ctx_len)
+    dev = _need_cuda(q_fp8, weights, kcache, kscale, block_table, ctx_len, out)
     B, H, D = q_fp8.shape
     if kcache.dtype != FP8 or q_fp8.dtype != FP8 or kcache.dim() != 2 or kcache.shape[1] != D:
         raise DsaError("kcache must be float8_e4m3fn [num_pages*64, D]")
@@ -122,27 +155,28 @@ def fp8_paged_mqa_logits(q_fp8, weights, kcache, kscale, block_table, ctx_len, m
     else:
         ld = out.stride(0)
     lib = _lib.load()
-    check(lib.dsa_indexer_logits_paged(_ptr(q_fp8), _ptr(weights), _w_dtype(weights), _ptr(kcache), _ptr(kscale),
-                                       _ptr(block_table), block_table.stride(0), _ptr(ctx_len), _ptr(out), ld,
-                                       B, H, D, kcache.shape[0] // 64, max_ctx,
-                                       _ptr(status_word(q_fp8.device)), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_indexer_logits_paged(_ptr(q_fp8), _ptr(weights), _w_dtype(weights), _ptr(kcache), _ptr(kscale),
+                                           _ptr(block_table), block_table.stride(0), _ptr(ctx_len), _ptr(out), ld,
+                                           B, H, D, kcache.shape[0] // 64, max_ctx,
+                                           _ptr(status_word(q_fp8.device)), _stream()))
     return out[:B, :max_ctx]
 
 
 def topk_select(logits: torch.Tensor, k: int, ks=None, ke=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Indices (int32, unsorted) of the k largest entries of each row's window
     [ks, ke); -1 padding when the window holds fewer than k columns."""
-    _need_cuda(logits, ks, ke)
+    dev = _need_cuda(logits, ks, ke, out)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise DsaError("logits must be fp32 [T, S] with unit column stride")
     T, S = logits.shape
     ks = _as_i32(ks, T, "ks")
     ke = _as_i32(ke, T, "ke")
-    if out is None:
-        out = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    out = _check_idx_out(out, T, k, logits.device)
     lib = _lib.load()
-    check(lib.dsa_topk_select(_ptr(logits), logits.stride(0) if T > 1 else max(S, logits.stride(0)), _ptr(ks),
-                              _ptr(ke), T, S, k, _ptr(out), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_topk_select(_ptr(logits), logits.stride(0) if T > 1 else max(S, logits.stride(0)), _ptr(ks),
+                                  _ptr(ke), T, S, k, _ptr(out), _stream()))
     return out
 
 
@@ -150,7 +184,7 @@ _workspaces = {}
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
-    key = torch.device(device).index or 0
+    key = _dev_index(device)
     w = _workspaces.get(key)
     if w is None or w.numel() < nbytes:
         _workspaces[key] = w = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{key}")
@@ -161,7 +195,7 @@ def indexer_topk(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, workspace: Opti
                  max_workspace_bytes: int = 8 << 30, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Indexer logits + top-k (IndexerSimulator.logits_step, sparse_attn/DSA.py:336-362)
     in one library call.  Returns int32 [T, min(k, S)]."""
-    _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke)
+    dev = _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke, workspace, out)
     T, H, D = q_fp8.shape
     S = k_fp8.shape[0]
     k = min(k, S)
@@ -174,11 +208,11 @@ def indexer_topk(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, workspace: Opti
         full = lib.dsa_indexer_topk_workspace_bytes(T, S)
         row = full // max(T, 1)
         workspace = _workspace(q_fp8.device, min(full, max(max_workspace_bytes, 256 * row)))
-    if out is None:
-        out = torch.empty(T, k, dtype=torch.int32, device=q_fp8.device)
-    check(lib.dsa_indexer_topk(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
-                               _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out), _ptr(workspace), workspace.numel(),
-                               _ptr(status_word(q_fp8.device)), _stream()))
+    out = _check_idx_out(out, T, k, q_fp8.device)
+    with torch.cuda.device(dev):
+        check(lib.dsa_indexer_topk(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
+                                   _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out), _ptr(workspace), workspace.numel(),
+                                   _ptr(status_word(q_fp8.device)), _stream()))
     return out
 
 
@@ -187,7 +221,7 @@ def indexer_topk_static(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, out: Opt
     64 MiB array built into the library (shared by every call on the device, so
     calls that overlap on the GPU race).  ``out`` should be passed by such callers;
     it is only created here when omitted.  Sizes beyond the array are refused."""
-    _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke)
+    dev = _need_cuda(q_fp8, k_fp8, k_scale, weights, ks, ke, out)
     T, H, D = q_fp8.shape
     S = k_fp8.shape[0]
     k = min(k, S)
@@ -198,19 +232,19 @@ def indexer_topk_static(q_fp8, k_fp8, k_scale, weights, ks, ke, k: int, out: Opt
         raise DsaError("k_scale must be fp32 with one entry per key")
     ks = _as_i32(ks, T, "ks")
     ke = _as_i32(ke, T, "ke")
-    if out is None:
-        out = torch.empty(T, k, dtype=torch.int32, device=q_fp8.device)
+    out = _check_idx_out(out, T, k, q_fp8.device)
     lib = _lib.load()
-    check(lib.dsa_indexer_topk_static(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
-                                      _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out),
-                                      _ptr(status_word(q_fp8.device)), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_indexer_topk_static(_ptr(q_fp8), _ptr(k_fp8), _ptr(k_scale), _ptr(weights), _w_dtype(weights),
+                                          _ptr(ks), _ptr(ke), T, S, H, D, k, _ptr(out),
+                                          _ptr(status_word(q_fp8.device)), _stream()))
     return out
 
 
 def sparse_mla_prefill(q, kv, idx, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Sparse MLA over selected latent-KV rows.  q [T,H,576] bf16, kv [S,576] bf16,
     idx [T,K] int32 (negative = empty slot).  Returns bf16 [T,H,512]."""
-    _need_cuda(q, kv, idx)
+    dev = _need_cuda(q, kv, idx, out)
     if q.dtype != torch.bfloat16 or kv.dtype != torch.bfloat16 or idx.dtype != torch.int32:
         raise DsaError("sparse_mla_prefill takes bf16 q/kv and int32 idx")
     if q.dim() != 3 or q.shape[2] != 576 or kv.dim() != 2 or kv.shape[1] != 576 or idx.dim() != 2 or idx.shape[0] != q.shape[0]:
@@ -220,8 +254,9 @@ def sparse_mla_prefill(q, kv, idx, scale: float, out: Optional[torch.Tensor] = N
     if out is None:
         out = torch.empty(T, H, 512, dtype=torch.bfloat16, device=q.device)
     lib = _lib.load()
-    check(lib.dsa_sparse_mla_prefill(_ptr(q), _ptr(kv), _ptr(idx), _ptr(out), T, H, kv.shape[0], idx.shape[1],
-                                     float(scale), _ptr(status_word(q.device)), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_sparse_mla_prefill(_ptr(q), _ptr(kv), _ptr(idx), _ptr(out), T, H, kv.shape[0], idx.shape[1],
+                                         float(scale), _ptr(status_word(q.device)), _stream()))
     return out
 
 
@@ -229,7 +264,7 @@ def block_sparse_attn(q, k, v, lut, num, sm_scale: float, out: Optional[torch.Te
     """Block-sparse multi-head attention with the reference's stand-in signature (sparse_attn/DSA.py:232-247):
     q, k, v [B, S, H, 128] bf16; lut [B, H, S/64, topk] int32 key-block ids per 64-row query block;
     num [B, H, S/64] int32 = how many entries of each list count.  Non-causal.  Returns bf16 [B, S, H, 128]."""
-    _need_cuda(q, k, v, lut, num)
+    dev = _need_cuda(q, k, v, lut, num, out)
     if any(t.dtype != torch.bfloat16 for t in (q, k, v)) or lut.dtype != torch.int32 or num.dtype != torch.int32:
         raise DsaError("block_sparse_attn takes bf16 q/k/v and int32 lut/num")
     if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
@@ -241,8 +276,9 @@ def block_sparse_attn(q, k, v, lut, num, sm_scale: float, out: Optional[torch.Te
     if out is None:
         out = torch.empty_like(q)
     lib = _lib.load()
-    check(lib.dsa_block_sparse_mha(_ptr(q), _ptr(k), _ptr(v), _ptr(lut), _ptr(num), _ptr(out), B, S, H, D,
-                                   lut.shape[3], float(sm_scale), _ptr(status_word(q.device)), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_block_sparse_mha(_ptr(q), _ptr(k), _ptr(v), _ptr(lut), _ptr(num), _ptr(out), B, S, H, D,
+                                       lut.shape[3], float(sm_scale), _ptr(status_word(q.device)), _stream()))
     return out
 
 
@@ -250,7 +286,7 @@ def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: O
                             out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode step over the paged FP8 latent cache.  q [B,H,576] bf16, cache uint8
     [num_pages*64, 656], block_table [B,P] int32, idx [B,K] int32 logical positions."""
-    _need_cuda(q, cache, block_table, idx)
+    dev = _need_cuda(q, cache, block_table, idx, out, workspace)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.uint8 or idx.dtype != torch.int32 or block_table.dtype != torch.int32:
         raise DsaError("sparse_mla_decode_paged takes bf16 q, uint8 cache, int32 block_table/idx")
     if cache.dim() != 2 or cache.shape[1] != 656 or cache.shape[0] % 64:
@@ -265,10 +301,11 @@ def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: O
     if workspace is None:
         need = lib.dsa_sparse_mla_decode_workspace_bytes(B, H, idx.shape[1])
         workspace = _workspace(q.device, need) if need else None
-    check(lib.dsa_sparse_mla_decode_paged(_ptr(q), _ptr(cache), _ptr(block_table), block_table.stride(0), _ptr(idx),
-                                          _ptr(out), B, H, idx.shape[1], cache.shape[0] // 64, max_ctx, float(scale),
-                                          _ptr(workspace), workspace.numel() if workspace is not None else 0,
-                                          _ptr(status_word(q.device)), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_sparse_mla_decode_paged(_ptr(q), _ptr(cache), _ptr(block_table), block_table.stride(0), _ptr(idx),
+                                              _ptr(out), B, H, idx.shape[1], cache.shape[0] // 64, max_ctx, float(scale),
+                                              _ptr(workspace), workspace.numel() if workspace is not None else 0,
+                                              _ptr(status_word(q.device)), _stream()))
     return out
 
 
@@ -400,7 +437,7 @@ def fp8_quant_per_block(x: torch.Tensor, block_size: int = 128):
     """One-kernel FP8 e4m3 quantiser with the reference's semantics (sparse_attn/DSA.py:102-132):
     returns (q float8_e4m3fn with x's shape, scale fp32); the scale drops its last dim when a row
     is one block.  x is bf16 or fp32 on a CUDA device."""
-    _need_cuda(x)
+    dev = _need_cuda(x)
     last = x.shape[-1]
     assert last % block_size == 0, f"last dim {last} not multiple of block {block_size}"
     if x.dtype not in (torch.float32, torch.bfloat16):
@@ -411,6 +448,7 @@ def fp8_quant_per_block(x: torch.Tensor, block_size: int = 128):
     q = torch.empty(x.shape, dtype=FP8, device=x.device)
     scale = torch.empty(n_blocks, dtype=torch.float32, device=x.device)
     lib = _lib.load()
-    check(lib.dsa_fp8_quant_per_block(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, n_blocks, block_size,
-                                      _ptr(q), _ptr(scale), _stream()))
+    with torch.cuda.device(dev):
+        check(lib.dsa_fp8_quant_per_block(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, n_blocks, block_size,
+                                          _ptr(q), _ptr(scale), _stream()))
     return q, (scale.view(x.shape[:-1]) if nb == 1 else scale.view(*x.shape[:-1], nb))

@@ -15,7 +15,9 @@ Recorded cases
                FULL descending order of every row (topk = S), which pins the
                scorer's values far more tightly than a top-k set would
   mod_*        DsaIndexer.forward (NeoX and interleaved RoPE) and
-               Dsv4Indexer.forward: weights, inputs, returned indices
+               Dsv4Indexer.forward: weights, inputs, returned indices; for the
+               DsaIndexer cases also the FP8 bytes, scales and head gates that
+               forward() hands to the scorer
 """
 import os
 import sys
@@ -88,6 +90,17 @@ def main(ref_root: str) -> None:
         out[f"mod_{tag}_k_norm_b"] = _u16(sd["k_norm.bias"])
         if "compressor.pool_proj.weight" in sd:
             out[f"mod_{tag}_pool_proj"] = _u16(sd["compressor.pool_proj.weight"])
+        else:
+            # the stage outputs forward() feeds to the scorer (projections -> RoPE -> FP8 quantiser)
+            q, k, w = mod.projections(x, ql)
+            q, k = mod.rope(q, k)
+            q8, qs = DSA.fp8_quant_per_block(q)
+            k8, ksc = DSA.fp8_quant_per_block(k)
+            out[f"mod_{tag}_q_fp8"] = _u8(q8)
+            out[f"mod_{tag}_q_scale"] = qs.detach().numpy()
+            out[f"mod_{tag}_k_fp8"] = _u8(k8)
+            out[f"mod_{tag}_k_scale"] = ksc.detach().numpy()
+            out[f"mod_{tag}_w"] = w.detach().numpy()
 
     mk = lambda name, cr, il: DSA.IndexerSpec(name=name, hidden_size=64, q_lora_rank=32,
                                               index_n_heads=4, index_head_dim=128,
@@ -103,4 +116,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    main(sys.argv[1])

@@ -182,16 +182,19 @@ def test_host_pipeline_submits_back_to_back():
 
 @pytest.mark.parametrize("T,S,window", [(300, 4096, "causal"), (1021, 9000, "random"), (64, 70000, "causal")])
 def test_register_weight_form_equals_general_kernel_bitwise(T, S, window):
-    """64 heads x 128 takes the register-weight kernel; DSA_IDX_RW=0 sends the same call through the general
-    kernel.  Same summation order per (token, key): the logits agree bit for bit, for fp32 and bf16 weights."""
-    import os
+    """64 heads x 128 takes the register-weight kernel; the test hook dsa_test_indexer_logits_general sends the
+    same call through the general kernel.  Same summation order per (token, key): the logits agree bit for
+    bit, for fp32 and bf16 weights."""
+    from llmdivedeep_b200 import _lib
     q8, k8, ksc, w, ks, ke = to_dev(*indexer_inputs(T, S, 64, 128, seed=T + S, window=window))
+    ld = (S + 3) // 4 * 4
     for wt in (w, w.bfloat16()):
         a = ops.fp8_mqa_logits(q8, (k8, ksc), wt, ks, ke).clone()
-        os.environ["DSA_IDX_RW"] = "0"
-        try:
-            b = ops.fp8_mqa_logits(q8, (k8, ksc), wt, ks, ke).clone()
-        finally:
-            os.environ.pop("DSA_IDX_RW", None)
+        bfull = torch.empty(T, ld, dtype=torch.float32, device="cuda")
+        _lib.check(_lib.load().dsa_test_indexer_logits_general(
+            q8.data_ptr(), k8.data_ptr(), ksc.data_ptr(), wt.data_ptr(), 1 if wt.dtype == torch.bfloat16 else 0,
+            ks.data_ptr(), ke.data_ptr(), bfull.data_ptr(), ld, T, S, 64, 128, 1,
+            ops.status_word("cuda").data_ptr(), torch.cuda.current_stream().cuda_stream))
+        b = bfull[:, :S]
         assert torch.equal(a.view(torch.int32), b.view(torch.int32))
     ops.check_status("cuda")

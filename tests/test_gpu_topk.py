@@ -116,13 +116,14 @@ def test_full_size_row_property():
 
 
 def _two_pass(x, k, ks=None, ke=None):
-    """The same call with the sampled single pass switched off (every row takes the two-pass path)."""
-    import os
-    os.environ["DSA_TOPK_NO_SAMPLE"] = "1"
-    try:
-        return ops.topk_select(x, k, ks, ke)
-    finally:
-        os.environ.pop("DSA_TOPK_NO_SAMPLE", None)
+    """The same call through the test hook that keeps every row on the two-pass path."""
+    from llmdivedeep_b200 import _lib
+    T, S = x.shape
+    out = torch.empty(T, k, dtype=torch.int32, device=x.device)
+    _lib.check(_lib.load().dsa_test_topk_select_two_pass(
+        x.data_ptr(), x.stride(0), None if ks is None else ks.data_ptr(), None if ke is None else ke.data_ptr(),
+        T, S, k, out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return out
 
 
 def _adversarial_rows(S, g):

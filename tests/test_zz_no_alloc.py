@@ -17,6 +17,10 @@ pytestmark = pytest.mark.gpu
 def test_static_scratch_matches_workspace_variant_twice():
     lib = _lib.load()
     assert lib.dsa_indexer_topk_static_max_bytes() == 64 << 20
+    # the start-up call such a host makes once per device: T = 0 launches nothing, but it looks up
+    # the array's device address, which is when the driver creates the 64 MiB on this GPU
+    assert lib.dsa_indexer_topk_static(None, None, None, None, 0, None, None, 0, 65536, 64, 128, 2048, None, None,
+                                       None) == 0
     first = to_dev(*indexer_inputs(300, 65536, 64, 128, seed=21, window="causal"))   # 2 chunks of the array
     second = to_dev(*indexer_inputs(513, 3000, 64, 128, seed=22, window="random"))
     for args, k in ((first, 512), (second, 256)):
