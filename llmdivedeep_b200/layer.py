@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from . import _lib, ops
+from . import _lib, ops, sharding
 
 
 class SparseMLA(nn.Module):
@@ -35,12 +35,280 @@ class SparseMLA(nn.Module):
         return ops.sparse_mla_prefill(q, kv, idx, self.softmax_scale)
 
 
+class DSALayer(nn.Module):
+    """One DSA attention layer from hidden states: lightning indexer -> top-k -> sparse MLA.
+
+    forward(x [T, hidden]) -> bf16 [T, n_heads, 512].  The indexer half is the reference's DsaIndexer
+    (sparse_attn/DSA.py:472-568) on this package's kernels; the attention half -- which the reference
+    only stands in for with a block-sparse MHA call (sparse_attn/DSA.py:208-249) -- is MQA over one
+    shared latent KV row per token (576 = 512 latent + 64 rope dims, V = the 512 latent dims),
+    restricted to the selected positions.  Projections are bias-free Linears like the reference's:
+        q_lora = q_a(x);  indices = indexer(x, q_lora);  q = wq(q_lora) -> [T, n_heads, 576];
+        kv = wkv(x) -> [T, 576];  out = SparseMLA(q, kv, indices).
+    Defaults are the small configuration the CPU reference run uses: hidden 1024, 4 indexer heads of
+    dim 64 (FP8 block 64), top-k 256, 16 query heads; weights ~ N(0, init_std^2), LayerNorm at 1 / 0."""
+
+    def __init__(self, hidden_size: int = 1024, q_lora_rank: int = 256, index_n_heads: int = 4,
+                 index_head_dim: int = 64, rope_head_dim: int = 64, index_topk: int = 256, n_heads: int = 16,
+                 softmax_scale: float = 192 ** -0.5, rope_interleave: bool = False, init_std: float = 0.02,
+                 dtype: torch.dtype = torch.bfloat16, seed: Optional[int] = None):
+        super().__init__()
+        from . import DSA
+        self.n_heads, self.dtype = n_heads, dtype
+        self.spec = DSA.IndexerSpec("dsa-layer", hidden_size, q_lora_rank, index_n_heads, index_head_dim,
+                                    rope_head_dim, index_topk, 1, rope_interleave)
+        self.q_a = nn.Linear(hidden_size, q_lora_rank, bias=False, dtype=dtype)
+        self.indexer = DSA.DsaIndexer(self.spec, dtype=dtype)
+        self.wq = nn.Linear(q_lora_rank, n_heads * 576, bias=False, dtype=dtype)
+        self.wkv = nn.Linear(hidden_size, 576, bias=False, dtype=dtype)
+        self.attn = SparseMLA(softmax_scale)
+        g = torch.Generator().manual_seed(seed) if seed is not None else None
+        with torch.no_grad():
+            for lin in (self.q_a, self.wq, self.wkv, self.indexer.wq_b, self.indexer.wk, self.indexer.weights_proj):
+                lin.weight.copy_((torch.randn(lin.weight.shape, generator=g) * init_std).to(dtype))
+
+    @torch.no_grad()
+    def stages(self, x: torch.Tensor) -> dict:
+        """forward() with every intermediate kept: q_lora, the indexer's selection (int32, -1 = unused
+        slot), the attention operands and the output."""
+        x = x.to(self.dtype)
+        T = x.shape[0]
+        q_lora = self.q_a(x)
+        idx = self.indexer(x, q_lora).to(torch.int32)
+        q = self.wq(q_lora).view(T, self.n_heads, 576)
+        kv = self.wkv(x)
+        out = self.attn(q, kv, idx)
+        return {"x": x, "q_lora": q_lora, "idx": idx, "q": q, "kv": kv, "out": out}
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.stages(x)["out"]
+
+
 @torch.no_grad()
 def dsa_prefill(q_idx_fp8, k_idx_fp8, k_scale, w, ks, ke, topk: int, q, kv, softmax_scale: float):
     """Prefill: indexer logits + top-k (one library call), then sparse MLA over the selection.
     Returns (idx int32 [T,k], out bf16 [T,H,512])."""
     idx = ops.indexer_topk(q_idx_fp8, k_idx_fp8, k_scale, w, ks, ke, topk)
     return idx, ops.sparse_mla_prefill(q, kv, idx, softmax_scale)
+
+
+class PrefillPipeline:
+    """Chunked DSA prefill of one sequence (batch 1, causal, S queries over S keys).
+
+    Per chunk of query rows: indexer logits + top-k (one library call over a reused logits workspace),
+    then sparse MLA over the selection.  With world > 1 the query rows are dealt to the ranks in
+    `block_rows`-row blocks round-robin (sharding.round_robin_blocks): a rank runs only its own blocks --
+    keys and latent KV are replicated, nothing is exchanged before the output -- and the attention output
+    of every finished chunk is all-gathered on a side stream, one collective per round of `world` blocks
+    straight into its place in the full output, while the next chunk computes.
+
+    Tensors given to run() hold the rank's rows in local order (for world == 1 that is the sequence
+    itself): q_idx [T_loc, Hi, Di] e4m3, w [T_loc, Hi], q [T_loc, H, 576] bf16; replicated k_idx [S, Di]
+    e4m3, k_scale [S], kv [S, 576] bf16; out_full [S, H, 512] bf16 is complete on every rank afterwards.
+    `select` / `attend` default to the library kernels; tests pass CPU stand-ins."""
+
+    def __init__(self, S: int, device, n_heads: int = 128, topk: int = 2048, chunk_rows: int = 4096,
+                 softmax_scale: float = 192 ** -0.5, rank: int = 0, world: int = 1, block_rows: int = 256,
+                 group=None, select=None, attend=None):
+        if chunk_rows % block_rows:
+            raise ValueError("chunk_rows must be a whole number of row blocks")
+        self.S, self.device, self.H, self.k = S, torch.device(device), n_heads, min(topk, S)
+        self.scale, self.rank, self.world, self.block, self.group = float(softmax_scale), rank, world, block_rows, group
+        self.blocks = sharding.round_robin_blocks(S, world, rank, block_rows)      # global [start, end) of local blocks
+        self.T_loc = sum(b - a for a, b in self.blocks)
+        self.pos = sharding.rows_of(self.blocks, device=self.device).to(torch.int32)   # global position of each local row
+        self.ks = torch.zeros(self.T_loc, dtype=torch.int32, device=self.device)
+        self.ke = self.pos + 1
+        per = chunk_rows // block_rows
+        self.chunks = []                               # (first local row, last local row, first local block, last local block)
+        row = 0
+        for b0 in range(0, len(self.blocks), per):
+            b1 = min(len(self.blocks), b0 + per)
+            n = sum(e - a for a, e in self.blocks[b0:b1])
+            self.chunks.append((row, row + n, b0, b1))
+            row += n
+        self.rows_max = max((c[1] - c[0] for c in self.chunks), default=0)
+        self.idx = torch.empty(self.T_loc, self.k, dtype=torch.int32, device=self.device)
+        self.cuda = self.device.type == "cuda"
+        self.select, self.attend = select or self._select, attend or self._attend
+        self.ws = None
+        if select is None and self.rows_max:
+            nbytes = _lib.load().dsa_indexer_topk_workspace_bytes(self.rows_max, S)
+            self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.local = None
+        if world > 1:
+            self.local = [torch.empty(self.rows_max, n_heads, 512, dtype=torch.bfloat16, device=self.device)
+                          for _ in range(2)]
+            self._gathered = [None, None]              # per local buffer: event after the collectives that read it
+            self.comm = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self.launches_per_run = 3 * len(self.chunks)   # indexer, top-k, sparse MLA per chunk
+
+    def _select(self, q_idx, k_idx, k_scale, w, ks, ke, k, out):
+        return ops.indexer_topk(q_idx, k_idx, k_scale, w, ks, ke, k, workspace=self.ws, out=out)
+
+    def _attend(self, q, kv, idx, scale, out):
+        return ops.sparse_mla_prefill(q, kv, idx, scale, out=out)
+
+    def _gather_chunk(self, out_full, local, b0, b1):
+        off = 0
+        for j in range(b0, b1):
+            a, e = self.blocks[j]
+            sharding.all_gather_round(out_full, local[off:off + (e - a)], j, self.S, self.world, self.block, self.group)
+            off += e - a
+
+    @torch.no_grad()
+    def run_chunk(self, c: int, q_idx, k_idx, k_scale, w, q, kv, out_full, out_chunk=None):
+        """Chunk c of run(): rows [a, b) of the local tensors (pass slices starting at a row 0 = a through
+        `q_idx`, `w`, `q` already cut to the chunk).  Returns the tensor holding the chunk's output."""
+        a, b, b0, b1 = self.chunks[c]
+        idx = self.idx[a:b]
+        self.select(q_idx, k_idx, k_scale, w, self.ks[a:b], self.ke[a:b], self.k, idx)
+        if self.world == 1:
+            dst = out_full[a:b] if out_chunk is None else out_chunk
+            self.attend(q, kv, idx, self.scale, dst)
+            return dst
+        slot = c & 1
+        main = torch.cuda.current_stream(self.device) if self.cuda else None
+        if self.cuda and self._gathered[slot] is not None:
+            main.wait_event(self._gathered[slot])      # the collectives that read this buffer two chunks ago
+        dst = self.local[slot][: b - a]
+        self.attend(q, kv, idx, self.scale, dst)
+        if not self.cuda:
+            self._gather_chunk(out_full, dst, b0, b1)
+            return dst
+        computed = torch.cuda.Event()
+        computed.record(main)
+        with torch.cuda.stream(self.comm):
+            self.comm.wait_event(computed)
+            self._gather_chunk(out_full, dst, b0, b1)
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+            self._gathered[slot] = ev
+        return dst
+
+    @torch.no_grad()
+    def run(self, q_idx, k_idx, k_scale, w, q, kv, out_full):
+        for c, (a, b, _, _) in enumerate(self.chunks):
+            self.run_chunk(c, q_idx[a:b], k_idx, k_scale, w[a:b], q[a:b], kv, out_full)
+        self.finish()
+        return out_full
+
+    def finish(self):
+        """The current stream waits for the output collectives issued so far."""
+        if self.world > 1 and self.cuda:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm)
+
+
+class HostPrefillPipeline:
+    """PrefillPipeline for inputs and outputs that live in (pinned) host memory: while chunk c computes,
+    chunk c+1's q_idx / w / q travel host -> device on a copy stream and chunk c-1's attention output
+    travels device -> host on another, so the PCIe time overlaps the kernels.  Host tensors hold the
+    rank's local rows (PrefillPipeline order); keys and latent KV are copied whole at the start of a call."""
+
+    def __init__(self, pipe: PrefillPipeline, idx_heads: int = 64, idx_dim: int = 128, w_dtype=torch.bfloat16):
+        self.p = pipe
+        dev, S, R, H = pipe.device, pipe.S, pipe.rows_max, pipe.H
+        self.k_idx = torch.empty(S, idx_dim, dtype=ops.FP8, device=dev)
+        self.k_scale = torch.empty(S, dtype=torch.float32, device=dev)
+        self.kv = torch.empty(S, 576, dtype=torch.bfloat16, device=dev)
+        self.q_idx = [torch.empty(R, idx_heads, idx_dim, dtype=ops.FP8, device=dev) for _ in range(2)]
+        self.w = [torch.empty(R, idx_heads, dtype=w_dtype, device=dev) for _ in range(2)]
+        self.q = [torch.empty(R, H, 576, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.out = [torch.empty(R, H, 512, dtype=torch.bfloat16, device=dev) for _ in range(2)] if pipe.world == 1 else None
+        self.copy_in = torch.cuda.Stream(device=dev)
+        self.copy_out = torch.cuda.Stream(device=dev)
+        self._slot_busy = [None, None]
+        self._out_busy = [None, None]
+        self._keys_busy = None
+        self._first = True
+
+    @torch.no_grad()
+    def submit(self, q_idx_h, k_idx_h, k_scale_h, w_h, q_h, kv_h, out_h, out_full=None):
+        """Enqueue one prefill.  out_h [T_loc, H, 512] (host) receives the rank's rows; out_full (device,
+        [S, H, 512]) is required when world > 1 and receives the gathered output.  Returns the event after
+        which out_h is complete; nothing waits on the host."""
+        p = self.p
+        main = torch.cuda.current_stream(p.device)
+        if self._first:
+            self.copy_in.wait_stream(main)
+            self.copy_out.wait_stream(main)
+            self._first = False
+        n = len(p.chunks)
+        ready = [torch.cuda.Event() for _ in range(n)]
+
+        def stage(c):
+            a, b, _, _ = p.chunks[c]
+            s = c & 1
+            with torch.cuda.stream(self.copy_in):
+                if c == 0:
+                    if self._keys_busy is not None:
+                        self.copy_in.wait_event(self._keys_busy)
+                    self.k_idx.copy_(k_idx_h, non_blocking=True)
+                    self.k_scale.copy_(k_scale_h, non_blocking=True)
+                    self.kv.copy_(kv_h, non_blocking=True)
+                if self._slot_busy[s] is not None:
+                    self.copy_in.wait_event(self._slot_busy[s])
+                self.q_idx[s][: b - a].copy_(q_idx_h[a:b], non_blocking=True)
+                self.w[s][: b - a].copy_(w_h[a:b], non_blocking=True)
+                self.q[s][: b - a].copy_(q_h[a:b], non_blocking=True)
+                ready[c].record(self.copy_in)
+
+        stage(0)
+        computed = None
+        for c, (a, b, _, _) in enumerate(p.chunks):
+            s = c & 1
+            if c + 1 < n:
+                stage(c + 1)
+            main.wait_event(ready[c])
+            if p.world == 1 and self._out_busy[s] is not None:
+                main.wait_event(self._out_busy[s])
+            dst = p.run_chunk(c, self.q_idx[s][: b - a], self.k_idx, self.k_scale, self.w[s][: b - a],
+                              self.q[s][: b - a], self.kv, out_full, out_chunk=None if p.world > 1 else self.out[s][: b - a])
+            computed = torch.cuda.Event()
+            computed.record(main)
+            self._slot_busy[s] = computed
+            with torch.cuda.stream(self.copy_out):
+                self.copy_out.wait_event(computed)
+                out_h[a:b].copy_(dst, non_blocking=True)
+                drained = torch.cuda.Event()
+                drained.record(self.copy_out)
+                if p.world == 1:
+                    self._out_busy[s] = drained
+                else:
+                    # the rank's local output buffer is also read by this copy: the next writer must wait for it
+                    if p._gathered[s] is not None:
+                        self.copy_out.wait_event(p._gathered[s])
+                    both = torch.cuda.Event()
+                    both.record(self.copy_out)
+                    p._gathered[s] = both
+        self._keys_busy = computed
+        p.finish()
+        done = torch.cuda.Event()
+        done.record(self.copy_out)
+        return done
+
+
+LATENT_TOKEN_BYTES = 656          # 512 e4m3 latent values, 4 fp32 group scales, 64 bf16 rope values
+
+
+@torch.no_grad()
+def pack_latent_cache(kv: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Latent KV rows [N, 576] (bf16 or fp32, CUDA) -> records of the paged FP8 latent cache, uint8
+    [N, 656]: the 512 latent values as e4m3 with one fp32 scale per 128 values (the indexer quantiser's
+    rule, sparse_attn/DSA.py:121-124: scale = max(absmax, 1e-6) / 448), then the 64 rope values as bf16.
+    This is the write side of the cache sparse_mla_decode_paged reads; rows go to
+    cache[block_table[b, pos // 64] * 64 + pos % 64]."""
+    N = kv.shape[0]
+    if kv.dim() != 2 or kv.shape[1] != 576:
+        raise ops.DsaError(f"latent KV must be [N, 576], got {tuple(kv.shape)}")
+    if out is None:
+        out = torch.empty(N, LATENT_TOKEN_BYTES, dtype=torch.uint8, device=kv.device)
+    q8, scale = ops.fp8_quant_per_block(kv[:, :512].contiguous(), 128)      # [N,512] e4m3, [N,4] fp32
+    out[:, :512] = q8.view(torch.uint8)
+    out[:, 512:528] = scale.contiguous().view(torch.uint8).view(N, 16)
+    out[:, 528:] = kv[:, 512:].to(torch.bfloat16).contiguous().view(torch.uint8).view(N, 128)
+    return out
 
 
 class DecodeWorkspace:

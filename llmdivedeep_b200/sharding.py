@@ -33,6 +33,17 @@ def row_chunks(n_rows: int, world: int, rank: int, chunk: int = 256) -> List[Tup
     return out
 
 
+def round_robin_blocks(n_rows: int, world: int, rank: int, block: int = 256) -> List[Tuple[int, int]]:
+    """[start, end) query-row ranges of `rank` when blocks of `block` rows are dealt round-robin
+    (block b -> rank b % world).  One round of `world` consecutive blocks is one all-gather that lands
+    in row order in the full output, so no re-ordering pass is needed afterwards; the causal cost of the
+    ranks differs by about 2 / rounds (rank world-1 always holds the latest block of a round)."""
+    if not (0 <= rank < world) or block <= 0:
+        raise ValueError("bad rank/world/block")
+    n_blocks = (n_rows + block - 1) // block
+    return [(b * block, min(n_rows, (b + 1) * block)) for b in range(rank, n_blocks, world)]
+
+
 def rows_of(chunks: List[Tuple[int, int]], device=None) -> torch.Tensor:
     """Row indices covered by a list of ranges, ascending."""
     if not chunks:
@@ -127,3 +138,21 @@ def all_gather_batch(local: torch.Tensor, batch: int, world: int, group=None) ->
     if all(b - a == pad for a, b in sizes):
         return gathered.reshape((batch,) + tuple(local.shape[1:]))
     return torch.cat([gathered[r][: b - a] for r, (a, b) in enumerate(sizes)], dim=0)
+
+
+def all_gather_round(out_full: torch.Tensor, local_block: torch.Tensor, round_index: int, n_rows: int, world: int,
+                     block: int = 256, group=None) -> None:
+    """One round of the round-robin block split: every rank contributes its block of round
+    `round_index` (rows [(round*world + rank)*block, ...)), and the `world` blocks land side by side, in
+    row order, in out_full[round*world*block : (round+1)*world*block].  A full round is ONE collective
+    straight into the output; the last, ragged round goes through a padded buffer."""
+    lo = round_index * world * block
+    hi = min(n_rows, lo + world * block)
+    if hi - lo == world * block:
+        _all_gather_flat(out_full[lo:hi], local_block, world, group)
+        return
+    buf = local_block.new_zeros((block,) + tuple(out_full.shape[1:]))
+    buf[: local_block.shape[0]] = local_block
+    gathered = local_block.new_empty((world * block,) + tuple(out_full.shape[1:]))
+    _all_gather_flat(gathered, buf, world, group)
+    out_full[lo:hi] = gathered[: hi - lo]

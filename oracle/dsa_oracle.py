@@ -142,12 +142,18 @@ def check_topk_sets(sel: np.ndarray, scores: np.ndarray, ks, ke, k: int,
                       wrong count, or a swap further than ``ulp_tol`` fp32 ulps
                       of the k-th score away from it),
       max_ulp         the largest distance, in fp32 ulps of the k-th score, of
-                      any swapped element from the k-th score.
+                      any swapped element from the k-th score,
+      swapped_rows    rows whose set differs from the checker's by near-ties,
+      rows_over_1ulp  how many of those have a swap further than 1.0 ulp away
+                      (whatever ``ulp_tol`` is): the count to report against a
+                      1-ulp contract.
     """
     T = sel.shape[0]
     exact = 0
     bad = []
     max_ulp = 0.0
+    swapped = 0
+    over1 = 0
     for t in range(T):
         lo, hi = int(ks[t]), int(ke[t])
         n_valid = max(0, hi - lo)
@@ -178,9 +184,12 @@ def check_topk_sets(sel: np.ndarray, scores: np.ndarray, ks, ke, k: int,
         ulp = float(np.spacing(np.float32(abs(thr)))) if thr != 0 else float(np.spacing(np.float32(1e-30)))
         d = max(thr - lowc, highd - thr, 0.0) / ulp
         max_ulp = max(max_ulp, d)
+        swapped += 1
+        over1 += d > 1.0
         if d > ulp_tol:
             bad.append(t)
-    return {"exact_rows": exact, "bad_rows": bad, "max_ulp": max_ulp, "rows": T}
+    return {"exact_rows": exact, "bad_rows": bad, "max_ulp": max_ulp, "rows": T,
+            "swapped_rows": swapped, "rows_over_1ulp": int(over1)}
 
 
 # --------------------------------------------------------------------------
