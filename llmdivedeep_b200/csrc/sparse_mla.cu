@@ -4,23 +4,26 @@
 // register_sparse_fa() (sparse_attn/DSA.py:208-249); the reference itself has no sparse-MLA
 // kernel, no latent cache and no decode path (sparse_attn/DSA.py:475-477).
 //
-// One CTA per (query token, half of the V dimension, group of up to 128 heads).
-//   * Q [128 heads x 576] arrives by TMA as nine 128-byte-swizzled K-major panels (A operand).
-//   * The selected KV rows are gathered 64 at a time into nine [64 keys x 64 dims] panels with
-//     the same swizzle: cp.async from the bf16 KV, or -- for the paged FP8 latent cache of
-//     decode -- 16-byte loads, e4m3 -> bf16 with the per-128 group scale, 16-byte stores.
-//     A panel is the K-major B operand of S = Q K^T and, read with an MN-major descriptor, the
-//     B operand of O += P V: the rows are gathered once and used twice.
-//   * tcgen05.mma kind::f16 (bf16 in, fp32 out): S [128 x 64] and O [128 x 256] live in tensor
-//     memory; P is written back to tensor memory as packed bf16 and is the A operand of P V.
-//   * Online softmax with one thread per head (= TMEM lane): the row maximum and sum are
-//     thread-local; O is rescaled in tensor memory only when the running maximum grows by more
-//     than 8 (in log2 units), which keeps every exponent <= 2^8.
-// The two CTAs of a token each recompute S (the 512 fp32 columns of a full O would fill tensor
-// memory on their own); they share nothing and need no cluster.
+// One CLUSTER of two CTAs per (query token, group of up to 128 heads).  The 576-dim row splits
+// into nine 64-dim panels: eight latent panels (they are also V) and the rope panel.  CTA c of the
+// pair owns latent panels 4c..4c+3 -- its half of V -- and half of the rope panel's contraction:
+//   * it gathers only those five panels of every selected row (40 KB per 64-key block instead of
+//     72 KB, four blocks in flight): TMA tile::gather4 from the bf16 KV, or -- for the paged FP8
+//     latent cache of decode -- 16-byte loads, e4m3 -> bf16 with the per-128 group scale;
+//   * its five Q panels live in tensor memory as the A operand, so Q.K^T reads no shared memory for
+//     Q, and it computes a PARTIAL score tile S_c = Q_c K_c^T (18 tcgen05.mma kind::f16 of N = 64
+//     instead of 36: back-to-back MMAs into one accumulator complete ~130 cycles apart whatever
+//     their N, and that chain is what bounded the kernel that computed all of S in both CTAs);
+//   * the two partial tiles (fp32 [128 heads x 64 keys], 32 KB) are exchanged through distributed
+//     shared memory with one bulk copy per block and direction; S = S_0 + S_1 is the same sum, bit
+//     for bit, on both sides, so both run the same online softmax (thread = head = TMEM lane) and
+//     hold the same P, which is the A operand (from tensor memory) of O_c += P V_c with the
+//     gathered panels read through an MN-major descriptor.
+// O is rescaled in tensor memory only when the running maximum grows by more than 8 (log2 units).
 //
-// Roles: warps 0-3 softmax / output (thread = head), warp 4 lane 0 MMA issuer (warp 4 owns the
-// TMEM allocation), warps 5-8 gather.  Every wait is bounded (dsa_common.cuh).
+// Roles: warps 0-3 softmax / output, warps 4-7 gather + score exchange, warp 8 lane 0 MMA issuer
+// (warp 8 owns the TMEM allocation).  Every wait is bounded (dsa_common.cuh); the two CTAs leave
+// together through a cluster barrier.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <cuda_fp8.h>
@@ -34,34 +37,25 @@ namespace dsa {
 constexpr int kMlaDqk = 576;
 constexpr int kMlaDv = 512;
 constexpr int kMlaDvHalf = 256;
-#ifndef DSA_MLA_BLK
-#define DSA_MLA_BLK 64
-#define DSA_MLA_BUFS 2
-#endif
-constexpr int kMlaBlk = DSA_MLA_BLK;              // keys per block
-constexpr int kMlaBufs = DSA_MLA_BUFS;            // KV buffers in shared memory
-constexpr int kMlaPanels = kMlaDqk / 64;          // 9 panels of 64 dims (128 bytes)
-constexpr int kMlaQTmemPanels = 5;                // Q panels kept in tensor memory as the A operand
-constexpr int kMlaQSmemPanels = kMlaPanels - kMlaQTmemPanels;   // the remaining 4 stay in shared memory
-constexpr int kMlaQPanelBytes = 128 * 128;        // 128 heads x 128 B
-constexpr int kMlaKPanelBytes = kMlaBlk * 128;    // 32 keys x 128 B
-constexpr int kMlaQBytes = kMlaPanels * kMlaQPanelBytes;   // 147456
-constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;   // 36864 per buffer
+constexpr int kMlaBlk = 64;                        // keys per block
+constexpr int kMlaPanels = 5;                      // panels per CTA: four latent (its V half) + rope
+constexpr int kMlaBufs = 4;                        // KV buffers in shared memory
+constexpr int kMlaQPanelBytes = 128 * 128;         // 128 heads x 128 B
+constexpr int kMlaKPanelBytes = kMlaBlk * 128;     // 64 keys x 128 B
+constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;      // 40960 per buffer
+constexpr int kMlaXBytes = 128 * kMlaBlk * 4;      // one partial score tile, fp32: 32768
+constexpr int kMlaRing = 6;                        // row-id slots (one per block in flight and a margin)
 constexpr int kMlaThreads = 288;
-constexpr int kMlaGatherThreads = 128;
-constexpr int kMlaMaxK = 2048;                    // selected slots per query (row ids staged in shared memory)
-constexpr int kMlaQSmemBytes = kMlaQSmemPanels * kMlaQPanelBytes;   // 65536
-constexpr int kMlaSmemBytes = 1024 + kMlaQSmemBytes + kMlaBufs * kMlaKBytes + 1024 + kMlaMaxK * 4;
-static_assert(kMlaBufs <= 2, "descriptor selection assumes one or two KV buffers");
-static_assert(kMlaBufs * kMlaKBytes >= kMlaQTmemPanels * kMlaQPanelBytes, "the KV buffers double as the staging area of the TMEM-bound Q panels");
-constexpr int kLatentTokenBytes = 656;            // 512 e4m3 + 4 fp32 scales + 64 bf16 rope
+constexpr int kMlaSmemBytes = 1024 + kMlaBufs * kMlaKBytes + 2 * kMlaXBytes + 512 + kMlaRing * kMlaBlk * 4;
+static_assert(kMlaSmemBytes <= 232448, "shared memory budget of one CTA");
+static_assert(kMlaKBytes >= kMlaQPanelBytes && kMlaXBytes == 2 * kMlaQPanelBytes, "Q staging: two panels in each exchange buffer, one in the last KV buffer");
+constexpr int kLatentTokenBytes = 656;             // 512 e4m3 + 4 fp32 scales + 64 bf16 rope
 constexpr int kLatentPage = 64;
-// tensor-memory columns
+// tensor-memory columns: O 256, S 64, P 32, Q 5 x 32
 constexpr uint32_t kColO = 0, kColS = 256, kColP = kColS + kMlaBlk, kColQ = kColP + kMlaBlk / 2, kMlaTmemCols = 512;
-static_assert(kColQ + kMlaQTmemPanels * 32 <= kMlaTmemCols, "tensor memory budget: O 256, S Blk, P Blk/2, Q 32 per panel");
+static_assert(kColQ + kMlaPanels * 32 <= kMlaTmemCols, "tensor memory budget");
 
 struct MlaArgs {
-  const __nv_bfloat16* kv;        // prefill: [S_kv, 576] bf16
   const uint8_t* cache;           // decode: [num_pages*64, 656] bytes
   const int32_t* block_table;     // decode: [B, table_stride]
   const int32_t* idx;             // [T, K] selected key positions (negative = empty)
@@ -77,13 +71,59 @@ struct MlaArgs {
   float* part_lse;                // [T * n_split, H] log2-sum-exp of each part (-inf = empty part)
 };
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-  const uint32_t n = valid ? 16u : 0u;            // 0 source bytes = zero fill
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+// ---- cluster helpers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+  return r;
 }
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+__device__ __forceinline__ void cluster_arrive_wait() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrive on the peer's barrier to say "I have READ the tiles".  Relaxed on purpose: a release at cluster scope
+// costs a memory fence of thousands of cycles per block, and nothing written by this thread has to become
+// visible -- the loads it orders were consumed by arithmetic that issued before this instruction, so they
+// have returned.
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// mbar_wait with cluster-scope acquire: for barriers the peer CTA arrives on or copies into
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (i > kFastSpins) {
+      if (*abort_flag) return false;
+      __nanosleep(40);
+    }
+  }
+  *abort_flag = 1;
+  if (status) atomicCAS(status, kStatusOk, kStatusWaitTimeout);
+  return false;
+}
+// this CTA's shared memory -> the peer's, completion counted on the peer's mbarrier
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, const void* src, uint32_t bytes, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(smem_u32(src)), "r"(bytes), "r"(bar_cluster) : "memory");
+}
+// four rows of a [rows, 576] bf16 tensor map (box 64 elements x 1 row), one 64-dim panel each -> 512 B of shared memory
+__device__ __forceinline__ void tma_gather4(void* dst, const void* tmap, int x, int r0, int r1, int r2, int r3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_u32(bar))
+      : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -94,109 +134,97 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
+// 16-byte chunk c (0..15) of row `row` of a partial score tile [128 rows x 256 B]: the chunk order is
+// rotated by the row inside each half so that the lanes of a warp hit different banks
+__device__ __forceinline__ int xchg_off(int row, int c) { return row * 256 + (((c & 8) | ((c ^ row) & 7)) << 4); }
 
-// Gather one block of selected rows into the nine swizzled panels of a buffer.  Thread g of 128.
-// rows_s: the block's row ids (prefill: kv row; decode: physical cache row), -1 = empty slot.
-template <bool FP8_PAGED>
-__device__ __forceinline__ void gather_block(const MlaArgs& a, const int* __restrict__ rows_s, uint8_t* kv_s, int g) {
-  if constexpr (!FP8_PAGED) {
-    // rows x 72 chunks of 16 bytes
-#pragma unroll 4
-    for (int q = g; q < kMlaBlk * 72; q += kMlaGatherThreads) {
-      const int r = q / 72, cc = q - r * 72;
-      const int p = cc >> 3, c = cc & 7;
-      const int row = rows_s[r];
-      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.kv) + (int64_t)max(row, 0) * (kMlaDqk * 2) + cc * 16;
-      cp_async16(kv_s + p * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4), src, row >= 0);
+// Paged FP8 latent cache: dequantise this CTA's panels of one block into a KV buffer.  Thread g of 128.
+// rows_s: physical cache row per slot, -1 = empty.
+__device__ __forceinline__ void dequant_block(const MlaArgs& a, const int* __restrict__ rows_s, uint8_t* kv_s, int g, int cta) {
+  constexpr int kRope = kMlaBlk * 8 / 128;          // rope chunks per thread
+  uint4 rope[kRope];
+#pragma unroll
+  for (int u = 0; u < kRope; ++u) {
+    const int q = g + u * 128;
+    const int row = rows_s[q >> 3];
+    rope[u] = make_uint4(0, 0, 0, 0);
+    if (row >= 0) rope[u] = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)row * kLatentTokenBytes + kMlaDv + 16) + (q & 7));
+  }
+  constexpr int kLat = kMlaBlk * 16 / 128;          // latent chunks (16 e4m3 values) per thread: this CTA's 256 dims
+  uint4 raw[kLat];
+  float sc[kLat];
+#pragma unroll
+  for (int u = 0; u < kLat; ++u) {
+    const int q = g + u * 128;
+    const int r = q >> 4, cc = q & 15;              // cc: 16-value chunk inside this CTA's 256 latent dims
+    const int row = rows_s[r];
+    raw[u] = make_uint4(0, 0, 0, 0);
+    sc[u] = 0.f;
+    if (row >= 0) {
+      const uint8_t* rec = a.cache + (int64_t)row * kLatentTokenBytes;
+      raw[u] = __ldg(reinterpret_cast<const uint4*>(rec + cta * kMlaDvHalf + cc * 16));
+      sc[u] = __ldg(reinterpret_cast<const float*>(rec + kMlaDv) + cta * 2 + (cc >> 3));
     }
-    cp_async_wait_all();
-  } else {
-    // latent: rows x 32 chunks of 16 e4m3 -> two 16-byte bf16 chunks each; rope: rows x 8 chunks.
-    // Every load of the block (rope, latent, scales) is issued before the first use: the cache does not
-    // fit L2, and this way a block pays one DRAM round trip instead of three.
-    constexpr int kRope = kMlaBlk * 8 / kMlaGatherThreads;     // rope chunks per thread
-    uint4 rope[kRope];
+  }
 #pragma unroll
-    for (int u = 0; u < kRope; ++u) {
-      const int q = g + u * kMlaGatherThreads;
-      const int row = rows_s[q >> 3];
-      rope[u] = make_uint4(0, 0, 0, 0);
-      if (row >= 0) rope[u] = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)row * kLatentTokenBytes + kMlaDv + 16) + (q & 7));
-    }
-    constexpr int kBatch = 16;
-    static_assert((kMlaBlk * 32) % (kMlaGatherThreads * kBatch) == 0, "latent chunks per thread must be a multiple of the batch");
-    for (int q0 = g; q0 < kMlaBlk * 32; q0 += kMlaGatherThreads * kBatch) {
-      uint4 raw[kBatch];
-      float sc[kBatch];
+  for (int u = 0; u < kLat; ++u) {
+    const int q = g + u * 128;
+    const int r = q >> 4, cc = q & 15;
+    const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+    uint32_t outw[8];
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const int q = q0 + u * kMlaGatherThreads;
-        const int r = q >> 5, cc = q & 31;           // cc: 16-element chunk of the 512 latent dims
-        const int row = rows_s[r];
-        raw[u] = make_uint4(0, 0, 0, 0);
-        sc[u] = 0.f;
-        if (row >= 0) {
-          const uint8_t* rec = a.cache + (int64_t)row * kLatentTokenBytes;
-          raw[u] = __ldg(reinterpret_cast<const uint4*>(rec + cc * 16));
-          sc[u] = __ldg(reinterpret_cast<const float*>(rec + kMlaDv) + (cc >> 3));
-        }
-      }
+    for (int i = 0; i < 4; ++i) {
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const int q = q0 + u * kMlaGatherThreads;
-        const int r = q >> 5, cc = q & 31;
-        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-        uint32_t outw[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const __nv_fp8x2_storage_t pr = static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * hh)) & 0xffffu);
-            const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3);
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-            outw[i * 2 + hh] = pack_bf16x2(f.x * sc[u], f.y * sc[u]);
-          }
-        }
-        const int d0 = cc * 16;                        // first latent dim of this chunk
-        const int p = d0 >> 6, c = (d0 & 63) >> 3;     // panel, 16-byte chunk inside the 128-byte row (even)
-        uint8_t* base = kv_s + p * kMlaKPanelBytes + r * 128;
-        *reinterpret_cast<uint4*>(base + ((c ^ (r & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-        *reinterpret_cast<uint4*>(base + (((c + 1) ^ (r & 7)) << 4)) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+      for (int hh = 0; hh < 2; ++hh) {
+        const __nv_fp8x2_storage_t pr = static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * hh)) & 0xffffu);
+        const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+        outw[i * 2 + hh] = pack_bf16x2(f.x * sc[u], f.y * sc[u]);
       }
     }
+    const int p = cc >> 2, c = (cc & 3) * 2;        // local panel, 16-byte chunk inside the 128-byte row (even)
+    uint8_t* base = kv_s + p * kMlaKPanelBytes + r * 128;
+    *reinterpret_cast<uint4*>(base + ((c ^ (r & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+    *reinterpret_cast<uint4*>(base + (((c + 1) ^ (r & 7)) << 4)) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+  }
 #pragma unroll
-    for (int u = 0; u < kRope; ++u) {
-      const int q = g + u * kMlaGatherThreads;
-      const int r = q >> 3, c = q & 7;
-      *reinterpret_cast<uint4*>(kv_s + 8 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = rope[u];
-    }
+  for (int u = 0; u < kRope; ++u) {
+    const int q = g + u * 128;
+    const int r = q >> 3, c = q & 7;
+    *reinterpret_cast<uint4*>(kv_s + 4 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = rope[u];
   }
   fence_async_smem();          // make the panel writes visible to the tensor core's reads
 }
 
 template <bool FP8_PAGED>
-__global__ void __launch_bounds__(kMlaThreads, 1)
-sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaThreads, 1)
+sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_s = smem;                               // Q panels 5..8 [128 heads x 128 B]
-  uint8_t* kv_s = q_s + kMlaQSmemBytes;              // KV buffers x 9 panels [Blk keys x 128 B]; first: staging of Q panels 0..4
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + kMlaBufs * kMlaKBytes);
+  uint8_t* kv_s = smem;                                        // four buffers x five panels [64 keys x 128 B]
+  uint8_t* send_s = kv_s + kMlaBufs * kMlaKBytes;              // this CTA's partial score tile
+  uint8_t* recv_s = send_s + kMlaXBytes;                       // the peer's
+  uint64_t* bars = reinterpret_cast<uint64_t*>(recv_s + kMlaXBytes);
   uint64_t* q_full = bars + 0;
-  uint64_t* o_final = bars + 1;
-  uint64_t* kv_full = bars + 2;                      // [2] gather -> MMA
-  uint64_t* kv_free = bars + 4;                      // [2] P.V of the block finished: its KV buffer is free
-  uint64_t* s_full = bars + 6;                       // [2] MMA -> softmax
-  uint64_t* p_full = bars + 8;                       // [2] softmax -> MMA
-  uint64_t* pv_done = bars + 10;                     // [2] P.V of block j finished: O is quiescent, P is free
-  uint64_t* s_free = bars + 12;                      // softmax has read S into registers
-  uint64_t* q_moved = bars + 13;                     // Q panels 0..4 are in tensor memory, the staging area is free
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* q_moved = bars + 1;                      // Q is in tensor memory, its staging areas are free
+  uint64_t* o_final = bars + 2;
+  uint64_t* s_full = bars + 3;                       // MMA -> exchange warps
+  uint64_t* s_free = bars + 4;                       // exchange warps have read S into registers
+  uint64_t* p_full = bars + 5;                       // softmax -> MMA
+  uint64_t* pv_done = bars + 6;                      // P.V of a block finished: O is quiescent, P is free
+  uint64_t* send_full = bars + 7;                    // this CTA's partial tile is in send_s
+  uint64_t* recv_full = bars + 8;                    // the peer's partial tile has landed in recv_s
+  uint64_t* xchg_free = bars + 9;                    // both softmax groups have read the tiles of the last exchange
+  uint64_t* kv_full = bars + 10;                     // [4] gather -> MMA
+  uint64_t* kv_free = bars + 14;                     // [4] P.V of the block finished: its KV buffer is free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_s = const_cast<int*>(abort_flag) + 1;
-  int* rows_all = reinterpret_cast<int*>(kv_s + kMlaBufs * kMlaKBytes + 1024);   // [kMlaMaxK] row id per slot, -1 = empty
+  int* ring = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 512);     // [kMlaRing][64] row id per slot, -1 = empty
 
-  const int t = blockIdx.x / a.n_split, split = blockIdx.x % a.n_split, vhalf = blockIdx.y, hg = blockIdx.z;
+  const int cta = blockIdx.x & 1, peer = cta ^ 1;              // rank in the cluster = V half = contraction part
+  const int unit = blockIdx.x >> 1;
+  const int t = unit / a.n_split, split = unit % a.n_split, hg = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_per = ((a.K + a.n_split - 1) / a.n_split + kMlaBlk - 1) / kMlaBlk * kMlaBlk;   // slots per part
   const int k_lo = min(a.K, split * k_per), k_cnt = min(a.K, k_lo + k_per) - k_lo;
@@ -205,61 +233,54 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(o_final, 1);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&kv_full[b], kMlaGatherThreads);
-      mbar_init(&kv_free[b], 1);
-      mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], 128);
-      mbar_init(&pv_done[b], 1);
-    }
-    mbar_init(s_free, 128);
     mbar_init(q_moved, 128);
+    mbar_init(o_final, 1);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 128);
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    mbar_init(send_full, 128);
+    mbar_init(recv_full, 1);
+    mbar_init(xchg_free, 8);                         // lane 0 of the four softmax warps of each CTA
+    for (int b = 0; b < kMlaBufs; ++b) {
+      mbar_init(&kv_full[b], FP8_PAGED ? 128 : 4);
+      mbar_init(&kv_free[b], 1);
+    }
     *abort_flag = 0;
     *last_s = -1;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
+    if constexpr (!FP8_PAGED) tma_prefetch_desc(&tmap_kv);
   }
   __syncthreads();
-  {  // translate every slot to a row id once; the last non-empty slot decides the number of key blocks
+  {  // the last usable slot decides the number of key blocks (the same number in both CTAs of the pair)
     int last = -1;
-    const int k_pad = (k_cnt + kMlaBlk - 1) / kMlaBlk * kMlaBlk;
-    for (int j = threadIdx.x; j < k_pad; j += kMlaThreads) {
-      int r = -1;
-      const int pos = j < k_cnt ? idx_row[j] : -1;
-      if (pos >= 0) {
-        if (pos >= a.S_kv) {
-          if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
-        } else if constexpr (!FP8_PAGED) {
-          r = pos;
-        } else {
-          const int phys = a.block_table[(int64_t)t * a.table_stride + pos / kLatentPage];
-          if (phys >= 0 && (int64_t)(phys + 1) * kLatentPage <= a.num_phys_rows) r = phys * kLatentPage + pos % kLatentPage;
-          else if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
-        }
-      }
-      rows_all[j] = r;
-      if (r >= 0) last = j;
+    for (int j = threadIdx.x; j < k_cnt; j += kMlaThreads) {
+      const int pos = idx_row[j];
+      if (pos >= 0 && pos < a.S_kv) last = j;
     }
     if (last >= 0) atomicMax(last_s, last);
   }
   __syncthreads();
   const int nblk = (*last_s + kMlaBlk) / kMlaBlk;
-  if (nblk == 0) {   // nothing selected: the output row is zero (a part: weight zero in the combine)
+  if (nblk == 0) {   // nothing selected: the output row is zero (a part: weight zero in the combine); no cluster traffic yet
     if (threadIdx.x < 128 && threadIdx.x < heads_here) {
       if (a.n_split == 1) {
-        uint4* o = reinterpret_cast<uint4*>(a.out + ((int64_t)t * a.H + hg * 128 + threadIdx.x) * kMlaDv + vhalf * kMlaDvHalf);
+        uint4* o = reinterpret_cast<uint4*>(a.out + ((int64_t)t * a.H + hg * 128 + threadIdx.x) * kMlaDv + cta * kMlaDvHalf);
         for (int c = 0; c < kMlaDvHalf * 2 / 16; ++c) o[c] = make_uint4(0, 0, 0, 0);
       } else {
-        const int64_t prow = (int64_t)blockIdx.x * a.H + hg * 128 + threadIdx.x;
-        float4* o = reinterpret_cast<float4*>(a.part_o + prow * kMlaDv + vhalf * kMlaDvHalf);
+        const int64_t prow = (int64_t)unit * a.H + hg * 128 + threadIdx.x;
+        float4* o = reinterpret_cast<float4*>(a.part_o + prow * kMlaDv + cta * kMlaDvHalf);
         for (int c = 0; c < kMlaDvHalf / 4; ++c) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (vhalf == 0) a.part_lse[prow] = -CUDART_INF_F;
+        if (cta == 0) a.part_lse[prow] = -CUDART_INF_F;
       }
     }
+    // an index that is out of range is still reported
+    for (int j = threadIdx.x; j < k_cnt; j += kMlaThreads)
+      if (idx_row[j] >= a.S_kv && a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
     return;
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, kMlaTmemCols);
     tmem_relinquish();
   }
@@ -267,112 +288,145 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  cluster_arrive_wait();          // the peer's barriers are initialised before anything is sent to it
 
-  if (warp == 4) {
+  // where the five Q panels wait for their move into tensor memory: two in each exchange buffer, one in the last KV buffer
+  auto q_stage = [&](int lp) -> uint8_t* {
+    return lp < 2 ? send_s + lp * kMlaQPanelBytes : lp < 4 ? recv_s + (lp - 2) * kMlaQPanelBytes : kv_s + (kMlaBufs - 1) * kMlaKBytes;
+  };
+
+  if (warp == 8) {
     // ------------------------------- MMA issuer -------------------------------
-    // Issue order: QK(0), then per block j: QK(j+1) (so the next scores are computed while
-    // the softmax of block j runs), wait for P(j), PV(j).  MMAs complete in issue order.
+    // Issue order: QK(0), QK(1), then QK(i), PV(i-2): the partial scores of a block travel to the peer and through the
+    // softmax while the next two blocks are scored.  MMAs complete in issue order.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(1, 1, 0, 0, 128, kMlaBlk);
       constexpr uint32_t idesc_pv = umma_idesc(1, 1, 0, 1, 128, kMlaDvHalf);
-      mbar_expect_tx(q_full, kMlaQBytes);
-      for (int p = 0; p < kMlaPanels; ++p)          // panels 0..4 into the staging area, 5..8 to their place; x in 4-byte units
-        tma_load_2d(p < kMlaQTmemPanels ? kv_s + p * kMlaQPanelBytes : q_s + (p - kMlaQTmemPanels) * kMlaQPanelBytes,
-                    &tmap_q, p * 32, t * a.H + hg * 128, q_full);
-      bool ok = mbar_wait(q_full, 0, abort_flag, a.status) && mbar_wait(q_moved, 0, abort_flag, a.status);
-      // The issuing thread is a single lane: every instruction between two MMAs delays the tensor pipe
-      // (a 64-key MMA takes ~48 cycles), so descriptors are built once and the 36 MMAs of a block are
-      // straight-line code with compile-time offsets.
-      uint64_t qdesc[kMlaQSmemPanels];
-#pragma unroll
-      for (int p = 0; p < kMlaQSmemPanels; ++p)
-        qdesc[p] = umma_smem_desc(smem_u32(q_s + p * kMlaQPanelBytes), 16, 1024, kSwz128);
-      uint64_t kdesc[kMlaBufs], vdesc_b[kMlaBufs];
+      mbar_expect_tx(q_full, kMlaPanels * kMlaQPanelBytes);
+      for (int lp = 0; lp < kMlaPanels; ++lp)        // x in 4-byte units: 32 per panel
+        tma_load_2d(q_stage(lp), &tmap_q, (lp < 4 ? cta * 4 + lp : 8) * 32, t * a.H + hg * 128, q_full);
+      bool ok = mbar_wait(q_moved, 0, abort_flag, a.status);
+      uint64_t kdesc[kMlaBufs], vdesc[kMlaBufs];
 #pragma unroll
       for (int b = 0; b < kMlaBufs; ++b) {
         kdesc[b] = umma_smem_desc(smem_u32(kv_s + b * kMlaKBytes), 16, 1024, kSwz128);
-        vdesc_b[b] = umma_smem_desc(smem_u32(kv_s + b * kMlaKBytes + vhalf * 4 * kMlaKPanelBytes), kMlaKPanelBytes, 1024, kSwz128);
+        vdesc[b] = umma_smem_desc(smem_u32(kv_s + b * kMlaKBytes), kMlaKPanelBytes, 1024, kSwz128);
       }
-      auto issue_qk = [&](int j) -> bool {
-        const int kvb = j % kMlaBufs;
-        if (!mbar_wait(&kv_full[kvb], (j / kMlaBufs) & 1, abort_flag, a.status)) return false;
-        if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, a.status)) return false;   // S of block j-1 was read
+      auto pick = [&](const uint64_t (&d)[kMlaBufs], int b) { return b == 0 ? d[0] : b == 1 ? d[1] : b == 2 ? d[2] : d[3]; };
+      const uint32_t rope_ks = 2 * cta;              // this CTA's two K-steps of the rope panel
+      // P.V of block j: four MMAs (N = 256) and the commits that release the block's KV buffer, P and O
+      auto pv_mmas = [&](int j) {
         tc_fence_after();
-        const uint64_t kd0 = kMlaBufs == 1 ? kdesc[0] : (kvb ? kdesc[kMlaBufs - 1] : kdesc[0]);
+        const uint64_t vd = pick(vdesc, j % kMlaBufs);
 #pragma unroll
-        for (int p = 0; p < kMlaPanels; ++p) {
-          const uint64_t kd = kd0 + uint64_t((p * kMlaKPanelBytes) >> 4);
+        for (int ks = 0; ks < kMlaBlk / 16; ++ks)     // 16 keys per step: 16 rows x 128 B further into each panel
+          umma_f16_ts(tmem + kColO, tmem + kColP + 8 * ks, vd + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
+        umma_commit(&kv_free[j % kMlaBufs]);
+        umma_commit(pv_done);
+        if (j == nblk - 1) umma_commit(o_final);
+      };
+      // Partial scores of block i.  The 18 MMAs form one dependent chain (about 130 cycles apart), so the tensor pipe
+      // idles three quarters of the time: P.V of block pv (< 0: none), whose P arrives while this chain runs, is
+      // slipped in at the first panel boundary after its P is there.  Returns false on a failed wait; pv = -1 once issued.
+      auto issue_qk = [&](int i, int& pv) -> bool {
+        const int kvb = i % kMlaBufs;
+        if (!mbar_wait(&kv_full[kvb], (i / kMlaBufs) & 1, abort_flag, a.status)) return false;
+        if (i > 0 && !mbar_wait(s_free, (i - 1) & 1, abort_flag, a.status)) return false;   // S of block i-1 was read
+        tc_fence_after();
+        const uint64_t kd0 = pick(kdesc, kvb);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            if (p < kMlaQTmemPanels)                 // A operand from tensor memory: no shared-memory read for Q
-              umma_f16_ts(tmem + kColS, tmem + kColQ + p * 32 + 8 * ks, kd + 2 * ks, idesc_qk, (p | ks) != 0);
-            else
-              umma_f16_ss(tmem + kColS, qdesc[p < kMlaQTmemPanels ? 0 : p - kMlaQTmemPanels] + 2 * ks, kd + 2 * ks, idesc_qk, 1);
+        for (int lp = 0; lp < 4; ++lp) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ts(tmem + kColS, tmem + kColQ + lp * 32 + 8 * ks, kd0 + uint64_t((lp * kMlaKPanelBytes) >> 4) + 2 * ks,
+                        idesc_qk, (lp | ks) != 0);
+          if (pv >= 0 && mbar_try_wait(p_full, pv & 1)) {
+            pv_mmas(pv);
+            pv = -1;
           }
         }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          umma_f16_ts(tmem + kColS, tmem + kColQ + 4 * 32 + 8 * (rope_ks + u),
+                      kd0 + uint64_t((4 * kMlaKPanelBytes) >> 4) + 2 * (rope_ks + u), idesc_qk, 1);
         umma_commit(s_full);
         return true;
       };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int b = j & 1, kvb = j % kMlaBufs;
-        // next scores first only if their keys have already landed; never stall P.V behind a gather
-        bool qk_done = j + 1 >= nblk;
-        if (!qk_done && kMlaBufs > 1 && mbar_try_wait(&kv_full[(j + 1) % kMlaBufs], ((j + 1) / kMlaBufs) & 1)) {
-          ok = issue_qk(j + 1);
-          qk_done = true;
+      for (int i = 0; i < nblk + 2 && ok; ++i) {
+        int pv = i >= 2 ? i - 2 : -1;
+        if (i < nblk) ok = issue_qk(i, pv);
+        if (ok && pv >= 0) {                           // not slipped in: its P comes later than the chain (or there is no chain left)
+          ok = mbar_wait(p_full, pv & 1, abort_flag, a.status);
+          if (ok) pv_mmas(pv);
         }
-        if (!ok) break;
-        ok = mbar_wait(p_full, j & 1, abort_flag, a.status);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t vdesc = kMlaBufs == 1 ? vdesc_b[0] : (kvb ? vdesc_b[kMlaBufs - 1] : vdesc_b[0]);
-#pragma unroll
-        for (int ks = 0; ks < kMlaBlk / 16; ++ks)     // 16 keys per step: 16 rows x 128 B further into each panel
-          umma_f16_ts(tmem + kColO, tmem + kColP + 8 * ks, vdesc + ks * (2048 >> 4), idesc_pv,
-                      (j | ks) != 0);
-        umma_commit(&kv_free[kvb]);
-        umma_commit(&pv_done[j & 1]);
-        if (j == nblk - 1) umma_commit(o_final);
-        if (!qk_done) ok = issue_qk(j + 1);
       }
     }
-  } else if (warp >= 5) {
-    // --------------------------------- gather ---------------------------------
-    const int g = threadIdx.x - 160;
-    mbar_wait(q_moved, 0, abort_flag, a.status);      // the buffers hold Q panels until they are in tensor memory
-    for (int j = 0; j < nblk; ++j) {
-      const int kvb = j % kMlaBufs;
-      mbar_wait(&kv_free[kvb], ((j / kMlaBufs) & 1) ^ 1, abort_flag, a.status);
-      gather_block<FP8_PAGED>(a, rows_all + j * kMlaBlk, kv_s + kvb * kMlaKBytes, g);
-      mbar_arrive(&kv_full[kvb]);
-      if (*abort_flag) break;
-    }
-  } else {
-    // ------------------------- softmax and output (thread = head) -------------------------
-    const int row = threadIdx.x;                       // 0..127 = TMEM lane
-    const uint32_t t_row = tmem + (uint32_t(warp * 32) << 16);
-    float m = -CUDART_INF_F, l = 0.f;
-    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, abort_flag, a.status));
-    if (ok) {
-      // this head's row of Q panels 0..4: swizzled shared memory -> packed bf16 pairs in tensor memory
-#pragma unroll 1
-      for (int p = 0; p < kMlaQTmemPanels; ++p) {
-        uint32_t qv[32];
-        const uint8_t* src = kv_s + p * kMlaQPanelBytes + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 w = *reinterpret_cast<const uint4*>(src + ((c ^ (row & 7)) << 4));
-          qv[4 * c + 0] = w.x; qv[4 * c + 1] = w.y; qv[4 * c + 2] = w.z; qv[4 * c + 3] = w.w;
-        }
-        tmem_st32(t_row + kColQ + p * 32, qv);
+  } else if (warp >= 4) {
+    // ----------------------- gather + exchange of the partial scores (thread = head) -----------------------
+    const int g = threadIdx.x - 128;                  // 0..127
+    const int w4 = warp - 4;
+    const uint32_t t_row = tmem + (uint32_t(w4 * 32) << 16);
+    const uint32_t peer_recv = mapa_u32(smem_u32(recv_s), peer), peer_recv_full = mapa_u32(smem_u32(recv_full), peer);
+    // Row ids travel two blocks ahead of their use, so that no global-memory latency sits in this loop: `pos_nxt` is the
+    // selected position of this thread's slot in the block after the next gather, `row_cur` the row id (for decode: the
+    // physical cache row, through the block table) of its slot in the next gather.  Threads 0..63 of the group.
+    auto load_pos = [&](int blk) -> int {
+      const int j = blk * kMlaBlk + g;
+      return (g < kMlaBlk && blk < nblk && j < k_cnt) ? __ldg(idx_row + j) : -1;
+    };
+    auto translate = [&](int pos) -> int {             // -1 = empty slot; bad positions and page ids are flagged and skipped
+      if (pos < 0) return -1;
+      if (pos >= a.S_kv) {
+        if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+        return -1;
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(q_moved);
-    }
-    for (int j = 0; j < nblk && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, a.status));
+      if constexpr (!FP8_PAGED) {
+        return pos;
+      } else {
+        const int phys = __ldg(a.block_table + (int64_t)t * a.table_stride + pos / kLatentPage);
+        if (phys >= 0 && (int64_t)(phys + 1) * kLatentPage <= a.num_phys_rows) return phys * kLatentPage + pos % kLatentPage;
+        if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+        return -1;
+      }
+    };
+    int row_cur = translate(load_pos(0)), pos_nxt = load_pos(1);
+    // stage the row ids of block i and fill its KV buffer; called for i = 0, 1, 2, ... in order
+    auto gather = [&](int i) -> bool {
+      const int kvb = i % kMlaBufs;
+      int* rows_s = ring + (i % kMlaRing) * kMlaBlk;
+      if (i >= kMlaBufs) mbar_wait(&kv_free[kvb], ((i / kMlaBufs) - 1) & 1, abort_flag, a.status);
+      if (g < kMlaBlk) rows_s[g] = row_cur;
+      row_cur = translate(pos_nxt);                    // block i+1: for decode its table entry is requested now, used next time
+      pos_nxt = load_pos(i + 2);
+      named_bar_sync(2, 128);                          // ids staged; every thread of the group takes the same way out of a failed wait
+      if (*abort_flag) return false;
+      uint8_t* dst = kv_s + kvb * kMlaKBytes;
+      if constexpr (FP8_PAGED) {
+        dequant_block(a, rows_s, dst, g, cta);
+        mbar_arrive(&kv_full[kvb]);
+      } else {
+        // warp w4 fetches rows 16*w4 .. 16*w4+15: lane = 5 * (group of four rows) + panel, one gather4 each
+        if (lane == 0) mbar_expect_tx(&kv_full[kvb], 4 * kMlaPanels * 512);
+        __syncwarp();
+        if (lane < 4 * kMlaPanels) {
+          const int rg = lane / kMlaPanels, lp = lane - rg * kMlaPanels;
+          const int r0 = w4 * 16 + rg * 4;
+          const int x = (lp < 4 ? cta * 4 + lp : 8) * 32;             // in the map's 4-byte elements
+          tma_gather4(dst + lp * kMlaKPanelBytes + r0 * 128, &tmap_kv, x, max(rows_s[r0], 0), max(rows_s[r0 + 1], 0),
+                      max(rows_s[r0 + 2], 0), max(rows_s[r0 + 3], 0), &kv_full[kvb]);
+        }
+      }
+      return true;
+    };
+    // Two blocks are fetched ahead: of the four buffers one belongs to the block whose P.V is pending, one to the block
+    // being scored, two to the blocks on their way.  (The last buffer holds a Q panel until Q is in tensor memory.)
+    constexpr int kAhead = 2;
+    bool ok = true;
+    for (int i = 0; i < min(nblk, kAhead) && ok; ++i) ok = gather(i);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(q_moved, 0, abort_flag, a.status));
+    for (int i = 0; i < nblk && ok; ++i) {
+      // partial scores of block i: tensor memory -> registers -> send_s -> the peer's recv_s
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, i & 1, abort_flag, a.status));
       if (!ok) break;
       tc_fence_after();
       uint32_t sv[kMlaBlk];
@@ -382,25 +436,90 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(s_free);                             // the next block's scores may overwrite S now
+      // both softmax groups must have read the tiles of block i-1 (i = 0: both have moved Q out of the buffers)
+      ok = __all_sync(0xffffffffu, mbar_wait_cluster(xchg_free, i & 1, abort_flag, a.status));
+      if (!ok) break;
+      if (g == 0) mbar_expect_tx(recv_full, kMlaXBytes);
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        *reinterpret_cast<uint4*>(send_s + xchg_off(g, c)) = make_uint4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
+      fence_async_smem();                              // the bulk copy reads send_s through the async proxy
+      mbar_arrive(send_full);
+      if (g == 0) {
+        ok = mbar_wait(send_full, i & 1, abort_flag, a.status);
+        if (ok) bulk_copy_to_peer(peer_recv, send_s, kMlaXBytes, peer_recv_full);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      // block i+2 goes into the buffer of block i-2, whose P.V has been slipped into the chain of block i: no wait here
+      if (ok && i + kAhead < nblk) ok = gather(i + kAhead);
+    }
+  } else {
+    // ------------------------- softmax and output (thread = head) -------------------------
+    const int row = threadIdx.x;                       // 0..127 = TMEM lane
+    const uint32_t t_row = tmem + (uint32_t(warp * 32) << 16);
+    const uint32_t peer_xchg_free = mapa_u32(smem_u32(xchg_free), peer);
+    float m = -CUDART_INF_F, l = 0.f;
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, abort_flag, a.status));
+    if (ok) {
+      // this head's row of the five Q panels: swizzled shared memory -> packed bf16 pairs in tensor memory
+#pragma unroll 1
+      for (int lp = 0; lp < kMlaPanels; ++lp) {
+        uint32_t qv[32];
+        const uint8_t* src = q_stage(lp) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 w = *reinterpret_cast<const uint4*>(src + ((c ^ (row & 7)) << 4));
+          qv[4 * c + 0] = w.x; qv[4 * c + 1] = w.y; qv[4 * c + 2] = w.z; qv[4 * c + 3] = w.w;
+        }
+        tmem_st32(t_row + kColQ + lp * 32, qv);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(q_moved);
+      __syncwarp();
+      if (lane == 0) {                                 // phase 0 of xchg_free: the staging areas of both CTAs are free
+        mbar_arrive(xchg_free);
+        mbar_arrive_remote_relaxed(peer_xchg_free);
+      }
+    }
+    for (int j = 0; j < nblk && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(send_full, j & 1, abort_flag, a.status) &&
+                                       mbar_wait_cluster(recv_full, j & 1, abort_flag, a.status));
+      if (!ok) break;
       float s[kMlaBlk];                                // raw scores; the (positive) scale is folded into the exponent's FMA
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const int off = xchg_off(row, c);
+        const float4 mine = *reinterpret_cast<const float4*>(send_s + off);
+        const float4 theirs = *reinterpret_cast<const float4*>(recv_s + off);
+        s[4 * c + 0] = mine.x + theirs.x; s[4 * c + 1] = mine.y + theirs.y;
+        s[4 * c + 2] = mine.z + theirs.z; s[4 * c + 3] = mine.w + theirs.w;
+      }
+      __syncwarp();
+      if (lane == 0) {                                 // both tiles are in registers: the next exchange may overwrite them
+        mbar_arrive(xchg_free);
+        mbar_arrive_remote_relaxed(peer_xchg_free);
+      }
       float bmax = -CUDART_INF_F;
-      const int* vrow = rows_all + j * kMlaBlk;
+      const int* vrow = ring + (j % kMlaRing) * kMlaBlk;
 #pragma unroll
       for (int i = 0; i < kMlaBlk; ++i) {
-        s[i] = vrow[i] >= 0 ? __uint_as_float(sv[i]) : -CUDART_INF_F;
+        s[i] = vrow[i] >= 0 ? s[i] : -CUDART_INF_F;
         bmax = fmaxf(bmax, s[i]);
       }
       bmax *= a.scale_log2e;
       const float m_new = fmaxf(m, bmax);
       const bool grow = m_new - m > 8.f;               // also true when m is still -inf and m_new is finite
+      bool waited_pv = false;
       if (__any_sync(0xffffffffu, grow)) {
         const float alpha = grow ? fast_exp2(m - m_new) : 1.f;
         if (grow) m = m_new;
         l *= alpha;
         if (j > 0) {
           // O must be quiescent: P.V of the previous block has to be complete
-          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
+          ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
           if (!ok) break;
+          waited_pv = true;
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < kMlaDvHalf; c += 32) {
@@ -423,8 +542,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         pk[i >> 1] = pack_bf16x2(p0, p1);
       }
       l += psum;
-      if (j > 0) {                                     // P is single-buffered: P.V of the previous block must be done
-        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status));
+      if (j > 0 && !waited_pv) {                       // P is single-buffered: P.V of the previous block must be done
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
         if (!ok) break;
         tc_fence_after();
       }
@@ -439,9 +558,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = a.out + ((int64_t)t * a.H + hg * 128 + row) * kMlaDv + vhalf * kMlaDvHalf;
-      const int64_t prow = (int64_t)blockIdx.x * a.H + hg * 128 + row;
-      if (a.n_split > 1 && vhalf == 0 && row < heads_here)
+      __nv_bfloat16* orow = a.out + ((int64_t)t * a.H + hg * 128 + row) * kMlaDv + cta * kMlaDvHalf;
+      const int64_t prow = (int64_t)unit * a.H + hg * 128 + row;
+      if (a.n_split > 1 && cta == 0 && row < heads_here)
         a.part_lse[prow] = l > 0.f ? m + log2f(l) : -CUDART_INF_F;
 #pragma unroll 1
       for (int c = 0; c < kMlaDvHalf; c += 32) {
@@ -449,7 +568,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
         tmem_ld32(t_row + kColO + c, ov);
         tmem_wait_ld();
         if (row < heads_here && a.n_split > 1) {
-          float4* po = reinterpret_cast<float4*>(a.part_o + prow * kMlaDv + vhalf * kMlaDvHalf + c);
+          float4* po = reinterpret_cast<float4*>(a.part_o + prow * kMlaDv + cta * kMlaDvHalf + c);
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             po[i >> 2] = make_float4(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv,
@@ -471,7 +590,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaArgs a) {
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (*abort_flag) {
+    // a wait gave up: let the copies that may still be in flight into this CTA land (bounded) before its shared memory goes away
+    if (threadIdx.x == 0)
+      for (int w = 0; w < 64; ++w) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_arrive_wait();          // neither CTA leaves while the other may still copy into it or arrive on its barriers
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, kMlaTmemCols);
   }
@@ -507,16 +633,20 @@ int make_tmap_2d_bytes(CUtensorMap* m, const void* base, uint64_t rows, uint64_t
                        uint32_t box_bytes, uint32_t box_rows);
 
 template <bool FP8_PAGED>
-static int launch_mla(const void* q, const MlaArgs& a, cudaStream_t stream) {
+static int launch_mla(const void* q, const void* kv, const MlaArgs& a, cudaStream_t stream) {
   if (a.T == 0 || a.H == 0) return DSA_OK;
-  CUtensorMap tq;
+  CUtensorMap tq, tkv;
   int rc = make_tmap_2d_bytes(&tq, q, (uint64_t)a.T * a.H, kMlaDqk * 2, kMlaDqk * 2, 128, 128);
   if (rc) return rc;
+  // rows of the bf16 KV, one 64-dim panel (128 bytes) of one row per box: the shape tile::gather4 takes
+  // (decode reads its cache with plain loads and only carries a copy of the Q map here)
+  if (FP8_PAGED || a.S_kv == 0) tkv = tq;
+  else if ((rc = make_tmap_2d_bytes(&tkv, kv, (uint64_t)a.S_kv, kMlaDqk * 2, kMlaDqk * 2, 128, 1))) return rc;
   auto kern = sparse_mla_kernel<FP8_PAGED>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes) != cudaSuccess)
     return set_error(DSA_ERR_CUDA, "sparse_mla: cannot raise dynamic shared memory to %d", kMlaSmemBytes);
-  const dim3 grid(a.T * a.n_split, 2, (a.H + 127) / 128);
-  kern<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tq, a);
+  const dim3 grid(2 * a.T * a.n_split, 1, (a.H + 127) / 128);
+  kern<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tq, tkv, a);
   if (a.n_split > 1) sparse_mla_combine_kernel<<<dim3(a.T, a.H), 128, 0, stream>>>(a);
   return check_launch("sparse_mla");
 }
@@ -524,20 +654,19 @@ static int launch_mla(const void* q, const MlaArgs& a, cudaStream_t stream) {
 int sparse_mla_prefill_launch(const void* q, const void* kv, const int32_t* idx, void* out, int T, int H, int S_kv,
                               int K, float scale, int32_t* status, cudaStream_t stream) {
   MlaArgs a{};
-  a.kv = static_cast<const __nv_bfloat16*>(kv);
   a.idx = idx;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.T = T; a.H = H; a.K = K; a.S_kv = S_kv;
   a.scale_log2e = scale * 1.4426950408889634f;
   a.status = status;
   a.n_split = 1;
-  return launch_mla<false>(q, a, stream);
+  return launch_mla<false>(q, kv, a, stream);
 }
 
 // With few queries (decode) one CTA pair per query leaves most SMs idle and walks 2048 slots serially:
 // cut the slot list into parts of >= 256 slots while the grid still fits the GPU in one wave.  More
-// parts than that lose: every part pays the CTA set-up again and writes an fp32 partial output that
-// the combine kernel reads back (batch 64 at 8 parts: 233 us; unsplit: 140 us; batch 8: 36 vs 116 us).
+// parts than that lose: every part pays the set-up again and writes an fp32 partial output that the
+// combine kernel reads back.
 int mla_decode_splits(int B, int H, int K) {
   const int ctas = B * 2 * ((H + 127) / 128);
   int ns = 1;
@@ -571,7 +700,7 @@ int sparse_mla_decode_launch(const void* q, const void* cache, const int32_t* bl
   a.num_phys_rows = num_pages * kLatentPage;
   a.scale_log2e = scale * 1.4426950408889634f;
   a.status = status;
-  return launch_mla<true>(q, a, stream);
+  return launch_mla<true>(q, nullptr, a, stream);
 }
 
 }  // namespace dsa
