@@ -21,8 +21,8 @@
 //     gathered panels read through an MN-major descriptor.
 // O is rescaled in tensor memory only when the running maximum grows by more than 8 (log2 units).
 //
-// Roles: warps 0-3 softmax / output, warps 4-7 gather + score exchange, warp 8 lane 0 MMA issuer
-// (warp 8 owns the TMEM allocation).  Every wait is bounded (dsa_common.cuh); the two CTAs leave
+// Roles: warps 0-3 softmax / output, warps 4-7 score exchange, warp 8 lane 0 MMA issuer (warp 8 owns the
+// TMEM allocation), warps 9-12 gather.  Every wait is bounded (dsa_common.cuh); the two CTAs leave
 // together through a cluster barrier.
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -45,7 +45,9 @@ constexpr int kMlaKPanelBytes = kMlaBlk * 128;     // 64 keys x 128 B
 constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;      // 40960 per buffer
 constexpr int kMlaXBytes = 128 * kMlaBlk * 4;      // one partial score tile, fp32: 32768
 constexpr int kMlaRing = 6;                        // row-id slots (one per block in flight and a margin)
-constexpr int kMlaThreads = 288;
+constexpr int kMlaGatherWarps = 4;                 // the TMA unit, not the issuing warps, bounds the gather: more warps do not help
+constexpr int kMlaGatherThreads = kMlaGatherWarps * 32;
+constexpr int kMlaThreads = 288 + kMlaGatherThreads;
 constexpr int kMlaSmemBytes = 1024 + kMlaBufs * kMlaKBytes + 2 * kMlaXBytes + 512 + kMlaRing * kMlaBlk * 4;
 static_assert(kMlaSmemBytes <= 232448, "shared memory budget of one CTA");
 static_assert(kMlaKBytes >= kMlaQPanelBytes && kMlaXBytes == 2 * kMlaQPanelBytes, "Q staging: two panels in each exchange buffer, one in the last KV buffer");
@@ -111,7 +113,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   if (status) atomicCAS(status, kStatusOk, kStatusWaitTimeout);
   return false;
 }
-// this CTA's shared memory -> the peer's, completion counted on the peer's mbarrier
+// this CTA's shared memory -> the peer's, completion counted on the peer's mbarrier.  (st.async from registers was
+// tried instead: 16-byte remote stores move a tile at about half the rate of this copy.)
 __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, const void* src, uint32_t bytes, uint32_t bar_cluster) {
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst_cluster), "r"(smem_u32(src)), "r"(bytes), "r"(bar_cluster) : "memory");
@@ -138,24 +141,24 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // rotated by the row inside each half so that the lanes of a warp hit different banks
 __device__ __forceinline__ int xchg_off(int row, int c) { return row * 256 + (((c & 8) | ((c ^ row) & 7)) << 4); }
 
-// Paged FP8 latent cache: dequantise this CTA's panels of one block into a KV buffer.  Thread g of 128.
+// Paged FP8 latent cache: dequantise this CTA's panels of one block into a KV buffer.  Thread g of kMlaGatherThreads.
 // rows_s: physical cache row per slot, -1 = empty.
 __device__ __forceinline__ void dequant_block(const MlaArgs& a, const int* __restrict__ rows_s, uint8_t* kv_s, int g, int cta) {
-  constexpr int kRope = kMlaBlk * 8 / 128;          // rope chunks per thread
+  constexpr int kRope = kMlaBlk * 8 / kMlaGatherThreads;          // rope chunks per thread
   uint4 rope[kRope];
 #pragma unroll
   for (int u = 0; u < kRope; ++u) {
-    const int q = g + u * 128;
+    const int q = g + u * kMlaGatherThreads;
     const int row = rows_s[q >> 3];
     rope[u] = make_uint4(0, 0, 0, 0);
     if (row >= 0) rope[u] = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)row * kLatentTokenBytes + kMlaDv + 16) + (q & 7));
   }
-  constexpr int kLat = kMlaBlk * 16 / 128;          // latent chunks (16 e4m3 values) per thread: this CTA's 256 dims
+  constexpr int kLat = kMlaBlk * 16 / kMlaGatherThreads;          // latent chunks (16 e4m3 values) per thread: this CTA's 256 dims
   uint4 raw[kLat];
   float sc[kLat];
 #pragma unroll
   for (int u = 0; u < kLat; ++u) {
-    const int q = g + u * 128;
+    const int q = g + u * kMlaGatherThreads;
     const int r = q >> 4, cc = q & 15;              // cc: 16-value chunk inside this CTA's 256 latent dims
     const int row = rows_s[r];
     raw[u] = make_uint4(0, 0, 0, 0);
@@ -168,7 +171,7 @@ __device__ __forceinline__ void dequant_block(const MlaArgs& a, const int* __res
   }
 #pragma unroll
   for (int u = 0; u < kLat; ++u) {
-    const int q = g + u * 128;
+    const int q = g + u * kMlaGatherThreads;
     const int r = q >> 4, cc = q & 15;
     const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
     uint32_t outw[8];
@@ -189,7 +192,7 @@ __device__ __forceinline__ void dequant_block(const MlaArgs& a, const int* __res
   }
 #pragma unroll
   for (int u = 0; u < kRope; ++u) {
-    const int q = g + u * 128;
+    const int q = g + u * kMlaGatherThreads;
     const int r = q >> 3, c = q & 7;
     *reinterpret_cast<uint4*>(kv_s + 4 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = rope[u];
   }
@@ -243,7 +246,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     mbar_init(recv_full, 1);
     mbar_init(xchg_free, 8);                         // lane 0 of the four softmax warps of each CTA
     for (int b = 0; b < kMlaBufs; ++b) {
-      mbar_init(&kv_full[b], FP8_PAGED ? 128 : 4);
+      mbar_init(&kv_full[b], FP8_PAGED ? kMlaGatherThreads : kMlaGatherWarps);
       mbar_init(&kv_free[b], 1);
     }
     *abort_flag = 0;
@@ -361,13 +364,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
       }
     }
-  } else if (warp >= 4) {
-    // ----------------------- gather + exchange of the partial scores (thread = head) -----------------------
-    const int g = threadIdx.x - 128;                  // 0..127
-    const int w4 = warp - 4;
-    const uint32_t t_row = tmem + (uint32_t(w4 * 32) << 16);
-    const uint32_t peer_recv = mapa_u32(smem_u32(recv_s), peer), peer_recv_full = mapa_u32(smem_u32(recv_full), peer);
-    // Row ids travel two blocks ahead of their use, so that no global-memory latency sits in this loop: `pos_nxt` is the
+  } else if (warp >= 9) {
+    // ----------------------------- gather of the selected rows -----------------------------
+    const int g = threadIdx.x - 288;                  // 0..kMlaGatherThreads-1
+    const int w4 = warp - 9;
+    // Row ids travel two blocks ahead of their use, so that no global-memory latency sits in the loop below: `pos_nxt` is the
     // selected position of this thread's slot in the block after the next gather, `row_cur` the row id (for decode: the
     // physical cache row, through the block table) of its slot in the next gather.  Threads 0..63 of the group.
     auto load_pos = [&](int blk) -> int {
@@ -398,19 +399,20 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (g < kMlaBlk) rows_s[g] = row_cur;
       row_cur = translate(pos_nxt);                    // block i+1: for decode its table entry is requested now, used next time
       pos_nxt = load_pos(i + 2);
-      named_bar_sync(2, 128);                          // ids staged; every thread of the group takes the same way out of a failed wait
+      named_bar_sync(2, kMlaGatherThreads);            // ids staged; every thread of the group takes the same way out of a failed wait
       if (*abort_flag) return false;
       uint8_t* dst = kv_s + kvb * kMlaKBytes;
       if constexpr (FP8_PAGED) {
         dequant_block(a, rows_s, dst, g, cta);
         mbar_arrive(&kv_full[kvb]);
       } else {
-        // warp w4 fetches rows 16*w4 .. 16*w4+15: lane = 5 * (group of four rows) + panel, one gather4 each
-        if (lane == 0) mbar_expect_tx(&kv_full[kvb], 4 * kMlaPanels * 512);
+        // warp w4 fetches kRowsPerWarp consecutive rows: lane = 5 * (group of four rows) + panel, one gather4 each
+        constexpr int kRowsPerWarp = kMlaBlk / kMlaGatherWarps, kLanes = kRowsPerWarp / 4 * kMlaPanels;
+        if (lane == 0) mbar_expect_tx(&kv_full[kvb], kLanes * 512);
         __syncwarp();
-        if (lane < 4 * kMlaPanels) {
+        if (lane < kLanes) {
           const int rg = lane / kMlaPanels, lp = lane - rg * kMlaPanels;
-          const int r0 = w4 * 16 + rg * 4;
+          const int r0 = w4 * kRowsPerWarp + rg * 4;
           const int x = (lp < 4 ? cta * 4 + lp : 8) * 32;             // in the map's 4-byte elements
           tma_gather4(dst + lp * kMlaKPanelBytes + r0 * 128, &tmap_kv, x, max(rows_s[r0], 0), max(rows_s[r0 + 1], 0),
                       max(rows_s[r0 + 2], 0), max(rows_s[r0 + 3], 0), &kv_full[kvb]);
@@ -418,12 +420,20 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       return true;
     };
-    // Two blocks are fetched ahead: of the four buffers one belongs to the block whose P.V is pending, one to the block
-    // being scored, two to the blocks on their way.  (The last buffer holds a Q panel until Q is in tensor memory.)
-    constexpr int kAhead = 2;
+    // Up to four blocks are in flight: the wait on kv_free inside gather() is what paces this loop.  The last buffer
+    // holds a Q panel until Q is in tensor memory.
     bool ok = true;
-    for (int i = 0; i < min(nblk, kAhead) && ok; ++i) ok = gather(i);
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(q_moved, 0, abort_flag, a.status));
+    for (int i = 0; i < nblk && ok; ++i) {
+      if (i == kMlaBufs - 1) mbar_wait(q_moved, 0, abort_flag, a.status);      // a failure shows in abort_flag inside gather()
+      ok = gather(i);
+    }
+  } else if (warp >= 4) {
+    // ----------------------- exchange of the partial scores (thread = head) -----------------------
+    const int g = threadIdx.x - 128;                  // 0..127
+    const int w4 = warp - 4;
+    const uint32_t t_row = tmem + (uint32_t(w4 * 32) << 16);
+    const uint32_t peer_recv = mapa_u32(smem_u32(recv_s), peer), peer_recv_full = mapa_u32(smem_u32(recv_full), peer);
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_moved, 0, abort_flag, a.status));     // Q panels wait in the exchange buffers
     for (int i = 0; i < nblk && ok; ++i) {
       // partial scores of block i: tensor memory -> registers -> send_s -> the peer's recv_s
       ok = __all_sync(0xffffffffu, mbar_wait(s_full, i & 1, abort_flag, a.status));
@@ -450,8 +460,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (ok) bulk_copy_to_peer(peer_recv, send_s, kMlaXBytes, peer_recv_full);
       }
       ok = __all_sync(0xffffffffu, ok);
-      // block i+2 goes into the buffer of block i-2, whose P.V has been slipped into the chain of block i: no wait here
-      if (ok && i + kAhead < nblk) ok = gather(i + kAhead);
     }
   } else {
     // ------------------------- softmax and output (thread = head) -------------------------
