@@ -113,8 +113,10 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   if (status) atomicCAS(status, kStatusOk, kStatusWaitTimeout);
   return false;
 }
-// this CTA's shared memory -> the peer's, completion counted on the peer's mbarrier.  (st.async from registers was
-// tried instead: 16-byte remote stores move a tile at about half the rate of this copy.)
+// this CTA's shared memory -> the peer's, completion counted on the peer's mbarrier.  One copy per tile.  Tried
+// instead and dropped: 16-byte st.async from registers (a tile takes ~2900 cycles against ~1650 for this copy), and
+// half a tile by each route (the st.async half then sits on the critical path of the softmax).  Also dropped: part
+// of the row gather by cp.async -- the load/store path moves rows no faster than gather4 and slows the softmax.
 __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, const void* src, uint32_t bytes, uint32_t bar_cluster) {
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst_cluster), "r"(smem_u32(src)), "r"(bytes), "r"(bar_cluster) : "memory");
@@ -414,8 +416,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const int rg = lane / kMlaPanels, lp = lane - rg * kMlaPanels;
           const int r0 = w4 * kRowsPerWarp + rg * 4;
           const int x = (lp < 4 ? cta * 4 + lp : 8) * 32;             // in the map's 4-byte elements
-          tma_gather4(dst + lp * kMlaKPanelBytes + r0 * 128, &tmap_kv, x, max(rows_s[r0], 0), max(rows_s[r0 + 1], 0),
-                      max(rows_s[r0 + 2], 0), max(rows_s[r0 + 3], 0), &kv_full[kvb]);
+          // an empty slot reads the row just past the end of the tensor: TMA fills it with zeros
+          auto rid = [&](int r) { const int v = rows_s[r]; return v >= 0 ? v : a.S_kv; };
+          tma_gather4(dst + lp * kMlaKPanelBytes + r0 * 128, &tmap_kv, x, rid(r0), rid(r0 + 1), rid(r0 + 2), rid(r0 + 3),
+                      &kv_full[kvb]);
         }
       }
       return true;
