@@ -55,6 +55,17 @@ const char* dsa_last_error_string(void);
 int dsa_fp8_quant_per_block(const void* x, int x_dtype, int64_t n_blocks, int block_size, void* q_fp8, float* scale,
                             void* stream);
 
+/* RoPE + per-row FP8 quantiser in one pass: stands in for DsaIndexer.rope followed by fp8_quant_per_block
+ * (sparse_attn/DSA.py:513-524, 530-531).  x_bf16 [n_rows, head_dim] (head_dim 64 or 128 = one FP8 block per
+ * row); row r is at position r / rows_per_pos (heads per token for q, 1 for k); cos_table / sin_table
+ * [n_pos, rope_dim / 2] fp32 as built by the reference's _rope_cossin (DSA.py:430-441).  The first rope_dim values
+ * of a row are rotated -- halves form (interleave = 0: fp32 products, not rounded, DSA.py:444-454) or even/odd
+ * pairs (interleave = 1: rounded to bf16, DSA.py:457-469) -- with the reference's operation order, then the row is
+ * quantised: bytes and scales equal the eager chain's. */
+int dsa_rope_fp8_quant(const void* x_bf16, int64_t n_rows, int head_dim, int rope_dim, int interleave, int rows_per_pos,
+                       const float* cos_table, const float* sin_table, int64_t n_pos, void* q_fp8, float* scale,
+                       void* stream);
+
 /* Lightning-indexer logits, contiguous keys.
  *   logits[t, s] = k_scale[s] * sum_h w[t,h] * relu(q[t,h,:] . k[s,:])  for ks[t] <= s < ke[t].
  * Stands in for deep_gemm.fp8_mqa_logits(q_fp8, (k_fp8, k_scale), w, ks, ke) as

@@ -236,16 +236,25 @@ class DsaIndexer(nn.Module):
         rd, il = self.spec.rope_head_dim, self.spec.rope_interleave
         return _rope_head(q, rd, q.shape[0], il), _rope_head(k, rd, k.shape[0], il)
 
+    def _rope_quant(self, x: torch.Tensor, n_pos: int, rows_per_pos: int):
+        """RoPE on the first rope_head_dim values of every head row, then the per-row FP8 quantiser: one fused kernel
+        for bf16 rows of one FP8 block (its bytes and scales equal the eager chain's), the eager chain otherwise."""
+        rd, il = self.spec.rope_head_dim, self.spec.rope_interleave
+        if x.dtype == torch.bfloat16 and x.shape[-1] == self._quant_block() and x.shape[-1] in (64, 128):
+            cos, sin = _rope_cossin(n_pos, rd, x.device)
+            return ops.rope_fp8_quant(x, cos, sin, rd, il, rows_per_pos)
+        return fp8_quant_per_block(_rope_head(x, rd, n_pos, il), self._quant_block())
+
     def _select(self, q, k, w, ke, topk: int) -> torch.Tensor:
-        q_fp8, q_scale = fp8_quant_per_block(q, self._quant_block())
-        k_fp8, k_scale = fp8_quant_per_block(k, self._quant_block())
+        """q [T,H,D], k [T_kv,D] straight from the projections (before RoPE), head gates w, windows ke."""
+        q_fp8, q_scale = self._rope_quant(q, q.shape[0], q.shape[1])
+        k_fp8, k_scale = self._rope_quant(k, k.shape[0], 1)
         ks = torch.zeros_like(ke)
         return _score_topk(q_fp8, k_fp8, k_scale, _fold(w, q_scale, self.spec.index_head_dim), ks, ke, topk)
 
     @torch.no_grad()
     def forward(self, x, q_lora_a):
         q, k, w = self.projections(x, q_lora_a)
-        q, k = self.rope(q, k)
         T = x.shape[0]
         ke = torch.arange(1, T + 1, dtype=torch.int32, device=x.device)
         return self._select(q, k, w, ke, min(self.spec.index_topk, T))
@@ -281,7 +290,5 @@ class Dsv4Indexer(DsaIndexer):
         q = self.wq_b(q_lora_a).view(T, self.spec.index_n_heads, self.spec.index_head_dim)
         k = self.k_norm(self.compressor(x))
         w = self.weights_proj(x).float() * self.spec.index_n_heads ** -0.5
-        rd, il = self.spec.rope_head_dim, self.spec.rope_interleave
-        q, k = _rope_head(q, rd, T, il), _rope_head(k, rd, T_kv, il)
         ke = ((torch.arange(1, T + 1, device=x.device) + cr - 1) // cr).to(torch.int32)
         return self._select(q, k, w, ke, min(self.spec.index_topk // cr, T_kv))

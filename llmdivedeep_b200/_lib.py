@@ -21,6 +21,8 @@ SIGNATURES = {
     "dsa_version": (c_int, []),
     "dsa_last_error_string": (c_char_p, []),
     "dsa_fp8_quant_per_block": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "dsa_rope_fp8_quant": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p,
+                                   c_void_p, c_void_p]),
     "dsa_indexer_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "dsa_indexer_logits_paged": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64,

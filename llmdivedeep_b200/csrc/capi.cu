@@ -63,6 +63,8 @@ int block_sparse_mha_launch(const void* q, const void* k, const void* v, const i
 
 int fp8_quant_launch(const void* x, int x_is_bf16, int64_t n_blocks, int block, void* q, float* scale,
                      cudaStream_t stream);
+int rope_fp8_quant_launch(const void* x, int64_t n_rows, int head_dim, int rope_dim, int interleave, int rows_per_pos,
+                          const float* cos_t, const float* sin_t, void* q, float* scale, cudaStream_t stream);
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -241,6 +243,26 @@ int dsa_fp8_quant_per_block(const void* x, int x_dtype, int64_t n_blocks, int bl
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q_fp8) & 3))
     return set_error(DSA_ERR_ALIGN, "fp8_quant_per_block: x must be 16-byte and q_fp8 4-byte aligned");
   return fp8_quant_launch(x, x_dtype == DSA_X_BF16, n_blocks, block_size, q_fp8, scale, static_cast<cudaStream_t>(stream));
+}
+
+int dsa_rope_fp8_quant(const void* x_bf16, int64_t n_rows, int head_dim, int rope_dim, int interleave, int rows_per_pos,
+                       const float* cos_table, const float* sin_table, int64_t n_pos, void* q_fp8, float* scale,
+                       void* stream) {
+  g_err[0] = 0;
+  if (n_rows < 0 || n_pos < 0) return set_error(DSA_ERR_SHAPE, "rope_fp8_quant: negative size");
+  if (n_rows == 0) return DSA_OK;
+  if (!x_bf16 || !cos_table || !sin_table || !q_fp8 || !scale) return set_error(DSA_ERR_ARG, "rope_fp8_quant: NULL pointer argument");
+  if (head_dim != 64 && head_dim != 128) return set_error(DSA_ERR_SHAPE, "rope_fp8_quant: head dim %d, only 64 and 128 are built", head_dim);
+  // the rotated part is made of whole lanes (head_dim / 32 values each) and, in the halves form, of two equal lane groups
+  const int per = head_dim / 32;
+  if (rope_dim <= 0 || rope_dim > head_dim || rope_dim % (2 * per)) return set_error(DSA_ERR_SHAPE, "rope_fp8_quant: rope_dim %d does not fit head dim %d", rope_dim, head_dim);
+  if (!interleave && ((rope_dim / 2 / per) & (rope_dim / 2 / per - 1))) return set_error(DSA_ERR_SHAPE, "rope_fp8_quant: rope_dim / 2 must span a power-of-two number of lanes");
+  if (rows_per_pos <= 0 || (n_rows + rows_per_pos - 1) / rows_per_pos > n_pos)
+    return set_error(DSA_ERR_SHAPE, "rope_fp8_quant: %lld rows at %d per position need more than the %lld positions of the tables",
+                     (long long)n_rows, rows_per_pos, (long long)n_pos);
+  if (!aligned16(x_bf16) || (reinterpret_cast<uintptr_t>(q_fp8) & 3)) return set_error(DSA_ERR_ALIGN, "rope_fp8_quant: x must be 16-byte and q_fp8 4-byte aligned");
+  return rope_fp8_quant_launch(x_bf16, n_rows, head_dim, rope_dim, interleave, rows_per_pos, cos_table, sin_table, q_fp8, scale,
+                               static_cast<cudaStream_t>(stream));
 }
 
 static const int kMinChunkRows = 256;

@@ -93,6 +93,32 @@ def dsa_prefill(q_idx_fp8, k_idx_fp8, k_scale, w, ks, ke, topk: int, q, kv, soft
     return idx, ops.sparse_mla_prefill(q, kv, idx, softmax_scale)
 
 
+class IndexShare:
+    """Index reuse across consecutive layers (GLM-5.2's IndexShare; the ``index_topk_freq`` by which the reference's
+    module driver divides the indexer time, bench_sparse_attention_modules.py:193): the indexer runs on every
+    ``freq``-th layer, and the layers in between attend over the indices of the last layer that ran it.
+
+        share = IndexShare(freq=4)
+        for i, layer in enumerate(layers):
+            idx = share.select(i, layer.indexer, x, q_lora)      # runs the indexer when i % 4 == 0
+            out = layer.attn(q, kv, idx)
+    """
+
+    def __init__(self, freq: int = 1):
+        if freq < 1:
+            raise ValueError("freq must be >= 1")
+        self.freq, self.idx, self.runs = int(freq), None, 0
+
+    def select(self, layer_idx: int, indexer, *inputs):
+        if self.idx is None or layer_idx % self.freq == 0:
+            self.idx = indexer(*inputs)
+            self.runs += 1
+        return self.idx
+
+    def reset(self):
+        self.idx = None
+
+
 class PrefillPipeline:
     """Chunked DSA prefill of one sequence (batch 1, causal, S queries over S keys).
 

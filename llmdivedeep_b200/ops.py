@@ -452,3 +452,26 @@ def fp8_quant_per_block(x: torch.Tensor, block_size: int = 128):
         check(lib.dsa_fp8_quant_per_block(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, n_blocks, block_size,
                                           _ptr(q), _ptr(scale), _stream()))
     return q, (scale.view(x.shape[:-1]) if nb == 1 else scale.view(*x.shape[:-1], nb))
+
+
+def rope_fp8_quant(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rope_dim: int, interleave: bool,
+                   rows_per_pos: int = 1):
+    """RoPE on the first ``rope_dim`` values of every head row followed by the per-row FP8 quantiser, one kernel
+    (DsaIndexer.rope + fp8_quant_per_block, sparse_attn/DSA.py:513-524, 530-531).  x bf16 [..., head_dim] with
+    head_dim 64 or 128; cos / sin fp32 [positions, rope_dim / 2]; the row with flat index r sits at position
+    r // rows_per_pos.  Returns (q float8_e4m3fn like x, scale fp32 x.shape[:-1]), bit-identical to the eager chain."""
+    dev = _need_cuda(x, cos, sin)
+    if x.dtype != torch.bfloat16 or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+        raise DsaError("rope_fp8_quant takes bf16 x and fp32 cos / sin tables")
+    D = x.shape[-1]
+    x, cos, sin = x.contiguous(), cos.contiguous(), sin.contiguous()
+    if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] * 2 != rope_dim:
+        raise DsaError(f"cos / sin must be [positions, {rope_dim // 2}], got {tuple(cos.shape)}")
+    n_rows = x.numel() // D
+    q = torch.empty(x.shape, dtype=FP8, device=x.device)
+    scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        check(lib.dsa_rope_fp8_quant(_ptr(x), n_rows, D, rope_dim, int(bool(interleave)), rows_per_pos, _ptr(cos), _ptr(sin),
+                                     cos.shape[0], _ptr(q), _ptr(scale), _stream()))
+    return q, scale

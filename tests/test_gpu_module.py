@@ -128,3 +128,35 @@ def test_deep_gemm_seam_returns_clean_logits():
     ref = O.indexer_logits_fp64(q8, k8, ksc, w, ks, ke).numpy()
     r = O.check_topk_sets(top, ref, ks.numpy(), ke.numpy(), 32, ulp_tol=ULP_TOL)
     assert not r["bad_rows"], r
+
+
+@pytest.mark.parametrize("D,rd,interleave", [(128, 64, False), (128, 64, True), (64, 64, False), (64, 32, True), (128, 128, False)])
+def test_fused_rope_quantiser_equals_the_eager_chain_bitwise(D, rd, interleave):
+    """dsa_rope_fp8_quant against RoPE with separate torch ops followed by the quantiser: on the GPU with the GPU's own
+    cos / sin tables (what the module does), and against the CPU oracle chain with the CPU's tables."""
+    T, H = 173, 5
+    g = torch.Generator().manual_seed(D + rd)
+    q = (torch.randn(T, H, D, generator=g) * 3).to(torch.bfloat16)
+    k = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    k[7] = 0
+    cos_c, sin_c = O.rope_cossin(T, rd)
+    for x, rpp in ((q, H), (k, 1)):
+        # CPU oracle chain, CPU tables
+        rot = (O.apply_rope_interleave if interleave else O.apply_rope_neox)(x[..., :rd], cos_c, sin_c)
+        want8, want_s = O.fp8_quant_per_block(torch.cat([rot, x[..., rd:]], dim=-1), D)
+        got8, got_s = ops.rope_fp8_quant(x.cuda(), cos_c.cuda(), sin_c.cuda(), rd, interleave, rpp)
+        assert torch.equal(got8.cpu().view(torch.uint8), want8.view(torch.uint8)) and torch.equal(got_s.cpu(), want_s)
+        # eager GPU chain, GPU tables
+        cos_g, sin_g = DSA._rope_cossin(T, rd, torch.device("cuda"))
+        e8, e_s = DSA.fp8_quant_per_block(DSA._rope_head(x.cuda(), rd, T, interleave), D)
+        f8, f_s = ops.rope_fp8_quant(x.cuda(), cos_g, sin_g, rd, interleave, rpp)
+        assert torch.equal(f8.view(torch.uint8), e8.view(torch.uint8)) and torch.equal(f_s, e_s)
+
+
+def test_fused_rope_quantiser_refuses_bad_shapes():
+    x = torch.zeros(4, 128, dtype=torch.bfloat16, device="cuda")
+    t = torch.zeros(4, 24, device="cuda")
+    with pytest.raises(ops.DsaError):
+        ops.rope_fp8_quant(x, t, t, 48, False)            # 24 dims per half = 6 lanes: not a power of two
+    with pytest.raises(ops.DsaError):
+        ops.rope_fp8_quant(x, t[:2, :16].contiguous(), t[:2, :16].contiguous(), 32, False)   # 4 rows, 2 positions

@@ -93,3 +93,19 @@ def test_index_output_must_have_the_kernel_stride():
                 torch.empty(6, 16, dtype=torch.int32)):
         with pytest.raises(ops.DsaError):
             ops._check_idx_out(bad, 6, 8, "cpu")
+
+
+def test_index_share_runs_the_indexer_every_freq_layers():
+    from llmdivedeep_b200 import layer
+    calls = []
+
+    def indexer(x):
+        calls.append(x)
+        return len(calls)
+
+    share = layer.IndexShare(freq=4)
+    got = [share.select(i, indexer, i) for i in range(10)]
+    assert calls == [0, 4, 8] and got == [1, 1, 1, 1, 2, 2, 2, 2, 3, 3] and share.runs == 3
+    assert [layer.IndexShare(1).select(i, indexer, i) for i in range(3)] == [4, 5, 6]
+    with pytest.raises(ValueError):
+        layer.IndexShare(0)
