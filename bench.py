@@ -742,6 +742,8 @@ def main():
                 "peak_source": f"2 x bf16_tflops_sustained of {peak_kind} peaks (fp8 dense = 2 x bf16; no fp8 entry is recorded; "
                                "the launches of one step run back to back for tens of ms)",
                 "ms_all_launches": ms_idx, "launches": len(pipe.chunks), "flops_all_launches": flops_idx,
+                "ms_per_launch": ms_idx / max(1, len(pipe.chunks)), "flops_per_launch": flops_idx / max(1, len(pipe.chunks)),
+                # traffic: the reduced case's logits partly stay in L2, so its DRAM bytes do not scale to a full launch
                 "traffic": None, "algorithmic_bytes": 4.0 * my_keys + pipe.T_loc * (HEADS * DIM + HEADS * 2) + S * 132.0}
     roof_mla = {"bound": "tensor", "kernel": "sparse_mla_kernel (bf16, 128 heads, qk 576 / v 512)",
                 "achieved": flops_mla / ms_mla / 1e9, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
@@ -750,8 +752,13 @@ def main():
                 "peak_source": f"bf16_tflops_sustained of {peak_kind} peaks (the launches of one step run back to back for "
                                "tens of ms)",
                 "ms_all_launches": ms_mla, "launches": len(pipe.chunks), "flops_all_launches": flops_mla,
-                "traffic": None,
+                "ms_per_launch": ms_mla / max(1, len(pipe.chunks)), "flops_per_launch": flops_mla / max(1, len(pipe.chunks)),
+                # dram__bytes_read + dram__bytes_write of one ncu capture of the 512-token reduced case (125.3 MB + 49.0 MB),
+                # scaled by the tokens of one launch: q, idx and the output grow with the tokens, the latent KV does not
+                "traffic": (125.29e6 + 48.97e6) * (pipe.T_loc / max(1, len(pipe.chunks))) / 512,
+                "traffic_source": "ncu capture of bench.py --case mla_prefill_small (512 tokens), scaled by tokens per launch",
                 "algorithmic_bytes": pipe.T_loc * MLA_HEADS * (576 + 512) * 2.0 + S * 1152.0 + pipe.T_loc * TOPK * 4.0,
+                "algorithmic_bytes_per_launch": (pipe.T_loc * (MLA_HEADS * (576 + 512) * 2.0 + TOPK * 4.0)) / max(1, len(pipe.chunks)) + S * 1152.0,
                 "l2_gather_bytes": my_pairs * 1152.0}
     tk_bytes = 4.0 * my_keys + pipe.T_loc * TOPK * 4.0
     roof_topk = {"bound": "hbm", "kernel": "topk_select_kernel", "achieved": tk_bytes / ms_topk / 1e6, "peak": peaks["hbm_gbs"],
