@@ -657,7 +657,8 @@ def main():
         saved = os.dup(1)
         os.dup2(2, 1)
         try:
-            dist.init_process_group("nccl", device_id=dev)
+            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)     # see layer.PrefillPipeline: the gathers overlap compute
+            dist.init_process_group("nccl", device_id=dev, pg_options=opts)
             dist.barrier()
             torch.cuda.synchronize()
         finally:

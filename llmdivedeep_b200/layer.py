@@ -167,7 +167,9 @@ class PrefillPipeline:
             self.local = [torch.empty(self.rows_max, n_heads, 512, dtype=torch.bfloat16, device=self.device)
                           for _ in range(2)]
             self._gathered = [None, None]              # per local buffer: event after the collectives that read it
-            self.comm = torch.cuda.Stream(device=self.device) if self.cuda else None
+            # high priority: the collective's CTAs are scheduled ahead of the attention kernel's waiting CTAs whenever an SM
+            # frees up (the attention kernel fills every SM's shared memory, so a collective cannot squeeze in beside it)
+            self.comm = torch.cuda.Stream(device=self.device, priority=-1) if self.cuda else None
         self.launches_per_run = 3 * len(self.chunks)   # indexer, top-k, sparse MLA per chunk
 
     def _select(self, q_idx, k_idx, k_scale, w, ks, ke, k, out):
