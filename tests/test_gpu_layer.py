@@ -87,3 +87,27 @@ def test_layer_matches_the_oracle_at_the_small_configuration():
     # when few keys are selected), and near-ties in the selection fall either way: bounded on average, not pointwise
     assert common > 0.97
     assert float(e2e.mean()) <= 2e-3 and float(e2e.max()) <= 0.25
+
+
+@torch.no_grad()
+def test_host_prefill_pipeline_equals_the_device_pipeline():
+    """Inputs and output in pinned host memory, chunks copied on side streams under the kernels: same result as the
+    device-resident pipeline, on two calls in a row (staging buffers are handed from call to call by events)."""
+    from tests.helpers import indexer_inputs
+    S, K, H = 1400, 256, 128
+    q8, k8, ksc, w, ks, ke = indexer_inputs(S, S, 64, 128, seed=60, window="causal", w_bf16=True)
+    g = torch.Generator().manual_seed(61)
+    q = torch.randn(S, H, 576, generator=g).to(torch.bfloat16)
+    kv = torch.randn(S, 576, generator=g).to(torch.bfloat16)
+    dev = torch.device("cuda", 0)
+    pipe = layer.PrefillPipeline(S, dev, n_heads=H, topk=K, chunk_rows=512, softmax_scale=0.05)
+    want = pipe.run(q8.to(dev), k8.to(dev), ksc.to(dev), w.to(dev), q.to(dev), kv.to(dev),
+                    torch.zeros(S, H, 512, dtype=torch.bfloat16, device=dev)).cpu()
+    hp = layer.HostPrefillPipeline(pipe, 64, 128, torch.bfloat16)
+    host = [t.pin_memory() for t in (q8, k8, ksc, w, q, kv)]
+    out_h = torch.zeros(S, H, 512, dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        out_h.zero_()
+        hp.submit(*host, out_h).synchronize()
+        assert torch.equal(out_h, want)
+    ops.check_status(dev)
