@@ -626,6 +626,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the sub-records and the incumbent comparison")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--chunk-rows", type=int, default=0, help="query rows per pipeline chunk (default: 4096 on one GPU, 2048 on several)")
     ap.add_argument("--seq", type=int, default=S_PREFILL,
                     help="prefill length; anything but 131072 is a reduced case for profiler captures, not a bench value")
     ap.add_argument("--case", default="headline",
@@ -676,7 +677,7 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    chunk_rows = 4096 if world == 1 else 2048
+    chunk_rows = args.chunk_rows or (4096 if world == 1 else 2048)
     pipe = layer.PrefillPipeline(S, dev, n_heads=MLA_HEADS, topk=TOPK, chunk_rows=chunk_rows, softmax_scale=SCALE,
                                  rank=rank, world=world, block_rows=BLOCK_ROWS)
     inputs = make_prefill_inputs(dev, 0, S, pipe.pos)
