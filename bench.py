@@ -806,8 +806,9 @@ def main():
         q8, k8, ksc, w, q, kv = (t.to(dev) for t in host)     # back on the device for the parity sample
         inputs = (q8, k8, ksc, w, q, kv)
         del hp, host, out_h
-        pipe.run(q8, k8, ksc, w, q, kv, out_full)
-        torch.cuda.synchronize()
+    # the per-kernel loops above reuse the pipeline's index and logit buffers: one more whole step for the parity sample
+    pipe.run(q8, k8, ksc, w, q, kv, out_full)
+    torch.cuda.synchronize()
 
     extras = {}
     if world > 1 and not args.no_extra and S == S_PREFILL:

@@ -14,16 +14,26 @@
 //     Q, and it computes a PARTIAL score tile S_c = Q_c K_c^T (18 tcgen05.mma kind::f16 of N = 64
 //     instead of 36: back-to-back MMAs into one accumulator complete ~130 cycles apart whatever
 //     their N, and that chain is what bounded the kernel that computed all of S in both CTAs);
-//   * the two partial tiles (fp32 [128 heads x 64 keys], 32 KB) are exchanged through distributed
-//     shared memory with one bulk copy per block and direction; S = S_0 + S_1 is the same sum, bit
-//     for bit, on both sides, so both run the same online softmax (thread = head = TMEM lane) and
-//     hold the same P, which is the A operand (from tensor memory) of O_c += P V_c with the
-//     gathered panels read through an MN-major descriptor.
+//   * the two partial tiles ([128 heads x 64 keys], rounded to fp16: 16 KB) are exchanged through
+//     distributed shared memory with one bulk copy per block and direction, double-buffered, issued
+//     by a warp of its own (the copy queues behind the gather on the SM's TMA unit, and the lane that
+//     issues it stalls for hundreds of cycles);
+//     S = fp16(S_0) + fp16(S_1), summed in fp32, is the same number, bit for bit, on both sides, so
+//     both run the same online softmax and hold the same P, which is the A operand (from tensor
+//     memory) of O_c += P V_c with the gathered panels read through an MN-major descriptor.  fp16
+//     partials carry 11 significant bits each: an error below the bf16 rounding of P for scores
+//     within +-65504; they halve the copy, which shares the TMA unit with the gather.
 // O is rescaled in tensor memory only when the running maximum grows by more than 8 (log2 units).
 //
-// Roles: warps 0-3 softmax / output, warps 4-7 score exchange, warp 8 lane 0 MMA issuer (warp 8 owns the
-// TMEM allocation), warps 9-12 gather.  Every wait is bounded (dsa_common.cuh); the two CTAs leave
-// together through a cluster barrier.
+// Roles: warps 0-7 exchange + softmax + output, warp 8 lane 0 MMA issuer (warp 8 owns the TMEM
+// allocation), warps 9-12 gather, warp 13 lane 0 issues the tile copies.  A thread of warps 0-7 owns one head (TMEM lane) and HALF of a
+// block's keys (warp w: lanes 32 (w % 4).., keys 32 (w / 4)..): with one thread per head and all 64
+// keys the softmax, not the tensor pipe, paced the kernel.  Per block n such a warp first moves its
+// part of the partial scores of block n out of tensor memory and on to the peer, then
+// runs the softmax of block n-1, whose peer tile arrived while the scores of block n were computed;
+// the two threads of a head agree on the block maximum through shared memory (rounded up to bf16:
+// any common reference point is exact for a softmax) and keep separate partial row sums.
+// Every wait is bounded (dsa_common.cuh); the two CTAs leave together through a cluster barrier.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <cuda_fp8.h>
@@ -43,14 +53,20 @@ constexpr int kMlaBufs = 4;                        // KV buffers in shared memor
 constexpr int kMlaQPanelBytes = 128 * 128;         // 128 heads x 128 B
 constexpr int kMlaKPanelBytes = kMlaBlk * 128;     // 64 keys x 128 B
 constexpr int kMlaKBytes = kMlaPanels * kMlaKPanelBytes;      // 40960 per buffer
-constexpr int kMlaXBytes = 128 * kMlaBlk * 4;      // one partial score tile, fp32: 32768
-constexpr int kMlaRing = 6;                        // row-id slots (one per block in flight and a margin)
+constexpr int kMlaXBytes = 128 * kMlaBlk * 2;      // one partial score tile, fp16: 16384
+constexpr int kMlaXStages = 2;                     // exchange buffers (send and receive) per CTA
+constexpr int kMlaRing = 2;                        // row-id slots: read only by the gather warps, inside the call that staged them
+constexpr int kMlaMaskRing = 8;                    // validity masks (64 bits per block) for the softmax: >= blocks in flight
 constexpr int kMlaGatherWarps = 4;                 // the TMA unit, not the issuing warps, bounds the gather: more warps do not help
 constexpr int kMlaGatherThreads = kMlaGatherWarps * 32;
-constexpr int kMlaThreads = 288 + kMlaGatherThreads;
-constexpr int kMlaSmemBytes = 1024 + kMlaBufs * kMlaKBytes + 2 * kMlaXBytes + 512 + kMlaRing * kMlaBlk * 4;
+constexpr int kMlaCopyWarp = 9 + kMlaGatherWarps;  // issues the copies of the partial score tiles
+constexpr int kMlaThreads = 288 + kMlaGatherThreads + 32;
+constexpr int kMlaBarBytes = 256;                  // mbarriers and a few words
+constexpr int kMlaPairBytes = 2 * 2 * 128 * 2;     // block maxima of the two key halves, double-buffered, bf16 (reused for the row sums, fp32)
+constexpr int kMlaSmemBytes = 1024 + kMlaBufs * kMlaKBytes + 2 * kMlaXStages * kMlaXBytes + kMlaBarBytes +
+                              kMlaRing * kMlaBlk * 4 + kMlaMaskRing * 2 * 4 + kMlaPairBytes;
 static_assert(kMlaSmemBytes <= 232448, "shared memory budget of one CTA");
-static_assert(kMlaKBytes >= kMlaQPanelBytes && kMlaXBytes == 2 * kMlaQPanelBytes, "Q staging: two panels in each exchange buffer, one in the last KV buffer");
+static_assert(2 * kMlaKBytes == kMlaPanels * kMlaQPanelBytes, "Q staging: the five panels fill the last two KV buffers");
 constexpr int kLatentTokenBytes = 656;             // 512 e4m3 + 4 fp32 scales + 64 bf16 rope
 constexpr int kLatentPage = 64;
 // tensor-memory columns: O 256, S 64, P 32, Q 5 x 32
@@ -82,40 +98,16 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta) {
 __device__ __forceinline__ void cluster_arrive_wait() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on the peer's barrier to say "I have READ the tiles".  Relaxed on purpose: a release at cluster scope
+// Arrive on the peer's barrier to say "I have READ the tile".  Relaxed on purpose: a release at cluster scope
 // costs a memory fence of thousands of cycles per block, and nothing written by this thread has to become
 // visible -- the loads it orders were consumed by arithmetic that issued before this instruction, so they
 // have returned.
 __device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// mbar_wait with cluster-scope acquire: for barriers the peer CTA arrives on or copies into
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (i > kFastSpins) {
-      if (*abort_flag) return false;
-      __nanosleep(40);
-    }
-  }
-  *abort_flag = 1;
-  if (status) atomicCAS(status, kStatusOk, kStatusWaitTimeout);
-  return false;
-}
-// this CTA's shared memory -> the peer's, completion counted on the peer's mbarrier.  One copy per tile.  Tried
-// instead and dropped: 16-byte st.async from registers (a tile takes ~2900 cycles against ~1650 for this copy), and
-// half a tile by each route (the st.async half then sits on the critical path of the softmax).  Also dropped: part
+// this CTA's shared memory -> the peer's, completion counted on the peer's mbarrier.  Tried instead and dropped:
+// 16-byte st.async from registers straight into the peer's buffer (no staging, no acknowledgement with four receive
+// stages, but the stores drain at about half the rate of this copy and hold up the warps that issue them), and part
 // of the row gather by cp.async -- the load/store path moves rows no faster than gather4 and slows the softmax.
 __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, const void* src, uint32_t bytes, uint32_t bar_cluster) {
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -139,9 +131,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
-// 16-byte chunk c (0..15) of row `row` of a partial score tile [128 rows x 256 B]: the chunk order is
-// rotated by the row inside each half so that the lanes of a warp hit different banks
-__device__ __forceinline__ int xchg_off(int row, int c) { return row * 256 + (((c & 8) | ((c ^ row) & 7)) << 4); }
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {      // out-of-range values saturate to +-65504
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// fp32 sums of two fp16 pairs, exact before the one rounding of each sum (mixed-precision adds: no separate conversions)
+__device__ __forceinline__ float2 add_f16x2_f32(uint32_t a, uint32_t b) {
+  float2 r;
+  asm("{\n\t.reg .b16 al, ah, bl, bh;\n\t.reg .f32 t0, t1;\n\t"
+      "mov.b32 {al, ah}, %2;\n\tmov.b32 {bl, bh}, %3;\n\t"
+      "add.rn.f32.f16 t0, al, 0f00000000;\n\tadd.rn.f32.f16 t1, ah, 0f00000000;\n\t"
+      "add.rn.f32.f16 %0, bl, t0;\n\tadd.rn.f32.f16 %1, bh, t1;\n\t}"
+      : "=f"(r.x), "=f"(r.y) : "r"(a), "r"(b));
+  return r;
+}
+// A partial score tile is [2 key halves][128 heads][32 keys] fp16: 64 bytes per thread of warps 0-7, 2 KB contiguous per
+// warp.  16-byte chunk c (0..3) of a thread's 64 bytes: the chunk order is rotated by the lane pair so that the eight lanes
+// of a quarter-warp hit different banks.
+__device__ __forceinline__ int xchg_off(int half, int row, int c) {
+  return half * (kMlaXBytes / 2) + row * 64 + (((c ^ (row >> 1)) & 3) << 4);
+}
+// fp32 -> bf16 bits, rounded towards +infinity
+__device__ __forceinline__ uint32_t bf16_bits_round_up(float x) {
+  const uint32_t b = __float_as_uint(x);
+  return ((b >> 31) || (b & 0x7fffffffu) >= 0x7f800000u) ? (b >> 16) : ((b + 0xffffu) >> 16);
+}
 
 // Paged FP8 latent cache: dequantise this CTA's panels of one block into a KV buffer.  Thread g of kMlaGatherThreads.
 // rows_s: physical cache row per slot, -1 = empty.
@@ -207,25 +222,27 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* kv_s = smem;                                        // four buffers x five panels [64 keys x 128 B]
-  uint8_t* send_s = kv_s + kMlaBufs * kMlaKBytes;              // this CTA's partial score tile
-  uint8_t* recv_s = send_s + kMlaXBytes;                       // the peer's
-  uint64_t* bars = reinterpret_cast<uint64_t*>(recv_s + kMlaXBytes);
+  uint8_t* send_s = kv_s + kMlaBufs * kMlaKBytes;              // [2] this CTA's partial score tiles
+  uint8_t* recv_s = send_s + kMlaXStages * kMlaXBytes;         // [2] the peer's
+  uint64_t* bars = reinterpret_cast<uint64_t*>(recv_s + kMlaXStages * kMlaXBytes);
   uint64_t* q_full = bars + 0;
   uint64_t* q_moved = bars + 1;                      // Q is in tensor memory, its staging areas are free
   uint64_t* o_final = bars + 2;
-  uint64_t* s_full = bars + 3;                       // MMA -> exchange warps
-  uint64_t* s_free = bars + 4;                       // exchange warps have read S into registers
+  uint64_t* s_full = bars + 3;                       // MMA -> warps 0-7
+  uint64_t* s_free = bars + 4;                       // warps 0-7 have read S into registers
   uint64_t* p_full = bars + 5;                       // softmax -> MMA
   uint64_t* pv_done = bars + 6;                      // P.V of a block finished: O is quiescent, P is free
-  uint64_t* send_full = bars + 7;                    // this CTA's partial tile is in send_s
-  uint64_t* recv_full = bars + 8;                    // the peer's partial tile has landed in recv_s
-  uint64_t* xchg_free = bars + 9;                    // both softmax groups have read the tiles of the last exchange
-  uint64_t* kv_full = bars + 10;                     // [4] gather -> MMA
-  uint64_t* kv_free = bars + 14;                     // [4] P.V of the block finished: its KV buffer is free
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* send_full = bars + 7;                    // [2] this CTA's partial tile is in send_s[stage]
+  uint64_t* recv_full = bars + 9;                    // [2] the peer's partial tile has landed in recv_s[stage]
+  uint64_t* xchg_free = bars + 11;                   // [2] the peer has read what this CTA sent into that stage
+  uint64_t* kv_full = bars + 13;                     // [4] gather -> MMA
+  uint64_t* kv_free = bars + 17;                     // [4] P.V of the block finished: its KV buffer is free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_s = const_cast<int*>(abort_flag) + 1;
-  int* ring = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 512);     // [kMlaRing][64] row id per slot, -1 = empty
+  int* ring = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + kMlaBarBytes);     // [kMlaRing][64] row id per slot, -1 = empty
+  uint32_t* masks = reinterpret_cast<uint32_t*>(ring + kMlaRing * kMlaBlk);        // [kMlaMaskRing][2] bit s = slot s of the block is in use
+  uint8_t* pair_s = reinterpret_cast<uint8_t*>(masks + kMlaMaskRing * 2);          // what the two threads of a head tell each other
 
   const int cta = blockIdx.x & 1, peer = cta ^ 1;              // rank in the cluster = V half = contraction part
   const int unit = blockIdx.x >> 1;
@@ -238,15 +255,17 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_moved, 128);
+    mbar_init(q_moved, 256);
     mbar_init(o_final, 1);
     mbar_init(s_full, 1);
-    mbar_init(s_free, 128);
-    mbar_init(p_full, 128);
+    mbar_init(s_free, 256);
+    mbar_init(p_full, 256);
     mbar_init(pv_done, 1);
-    mbar_init(send_full, 128);
-    mbar_init(recv_full, 1);
-    mbar_init(xchg_free, 8);                         // lane 0 of the four softmax warps of each CTA
+    for (int st = 0; st < kMlaXStages; ++st) {
+      mbar_init(&send_full[st], 8);                  // lane 0 of warps 0-7
+      mbar_init(&recv_full[st], 1);
+      mbar_init(&xchg_free[st], 8);                  // lane 0 of the peer's warps 0-7
+    }
     for (int b = 0; b < kMlaBufs; ++b) {
       mbar_init(&kv_full[b], FP8_PAGED ? kMlaGatherThreads : kMlaGatherWarps);
       mbar_init(&kv_free[b], 1);
@@ -295,15 +314,13 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tmem = *tmem_slot;
   cluster_arrive_wait();          // the peer's barriers are initialised before anything is sent to it
 
-  // where the five Q panels wait for their move into tensor memory: two in each exchange buffer, one in the last KV buffer
-  auto q_stage = [&](int lp) -> uint8_t* {
-    return lp < 2 ? send_s + lp * kMlaQPanelBytes : lp < 4 ? recv_s + (lp - 2) * kMlaQPanelBytes : kv_s + (kMlaBufs - 1) * kMlaKBytes;
-  };
+  // the five Q panels wait in the last two KV buffers for their move into tensor memory
+  auto q_stage = [&](int lp) -> uint8_t* { return kv_s + (kMlaBufs - 2) * kMlaKBytes + lp * kMlaQPanelBytes; };
 
   if (warp == 8) {
     // ------------------------------- MMA issuer -------------------------------
-    // Issue order: QK(0), QK(1), then QK(i), PV(i-2): the partial scores of a block travel to the peer and through the
-    // softmax while the next two blocks are scored.  MMAs complete in issue order.
+    // The partial scores of a block travel to the peer and through the softmax while the next blocks are scored: P.V of a
+    // block is issued about two blocks after its scores.  MMAs complete in issue order.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(1, 1, 0, 0, 128, kMlaBlk);
       constexpr uint32_t idesc_pv = umma_idesc(1, 1, 0, 1, 128, kMlaDvHalf);
@@ -331,39 +348,60 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (j == nblk - 1) umma_commit(o_final);
       };
       // Partial scores of block i.  The 18 MMAs form one dependent chain (about 130 cycles apart), so the tensor pipe
-      // idles three quarters of the time: P.V of block pv (< 0: none), whose P arrives while this chain runs, is
-      // slipped in at the first panel boundary after its P is there.  Returns false on a failed wait; pv = -1 once issued.
-      auto issue_qk = [&](int i, int& pv) -> bool {
-        const int kvb = i % kMlaBufs;
-        if (!mbar_wait(&kv_full[kvb], (i / kMlaBufs) & 1, abort_flag, a.status)) return false;
-        if (i > 0 && !mbar_wait(s_free, (i - 1) & 1, abort_flag, a.status)) return false;   // S of block i-1 was read
+      // idles three quarters of the time: P.V of block `pv`, if its P arrives while this chain is issued, is slipped in
+      // at the next panel boundary.
+      int qk = 0, pv = 0;                              // next block to score, next block to accumulate
+      auto pv_ready = [&]() { return pv < qk && mbar_try_wait(p_full, pv & 1); };
+      auto issue_qk = [&](int i) {
         tc_fence_after();
-        const uint64_t kd0 = pick(kdesc, kvb);
+        const uint64_t kd0 = pick(kdesc, i % kMlaBufs);
 #pragma unroll
         for (int lp = 0; lp < 4; ++lp) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             umma_f16_ts(tmem + kColS, tmem + kColQ + lp * 32 + 8 * ks, kd0 + uint64_t((lp * kMlaKPanelBytes) >> 4) + 2 * ks,
                         idesc_qk, (lp | ks) != 0);
-          if (pv >= 0 && mbar_try_wait(p_full, pv & 1)) {
-            pv_mmas(pv);
-            pv = -1;
-          }
+          if (pv_ready()) pv_mmas(pv++);
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u)
           umma_f16_ts(tmem + kColS, tmem + kColQ + 4 * 32 + 8 * (rope_ks + u),
                       kd0 + uint64_t((4 * kMlaKPanelBytes) >> 4) + 2 * (rope_ks + u), idesc_qk, 1);
         umma_commit(s_full);
-        return true;
       };
-      for (int i = 0; i < nblk + 2 && ok; ++i) {
-        int pv = i >= 2 ? i - 2 : -1;
-        if (i < nblk) ok = issue_qk(i, pv);
-        if (ok && pv >= 0) {                           // not slipped in: its P comes later than the chain (or there is no chain left)
-          ok = mbar_wait(p_full, pv & 1, abort_flag, a.status);
-          if (ok) pv_mmas(pv);
+      // Whatever is ready goes first: P.V of the oldest block whose P is there, else the scores of the next block (its
+      // rows gathered, S read out by warps 0-7).  Blocking on one of the two while the other could run is what used to
+      // pace the kernel: the softmax of a block ends about as late as the chain two blocks on.
+      uint32_t idle = 0;
+      while (ok && pv < nblk) {
+        if (pv_ready()) {
+          pv_mmas(pv++);
+          idle = 0;
+        } else if (qk < nblk && mbar_try_wait(&kv_full[qk % kMlaBufs], (qk / kMlaBufs) & 1) &&
+                   (qk == 0 || mbar_try_wait(s_free, (qk - 1) & 1))) {
+          issue_qk(qk);
+          ++qk;
+          idle = 0;
+        } else if (++idle > kFastSpins) {              // bounded like every other wait (dsa_common.cuh)
+          if (*abort_flag) ok = false;
+          else if (idle > kSpinLimit) {
+            *abort_flag = 1;
+            if (a.status) atomicCAS(a.status, kStatusOk, kStatusWaitTimeout);
+            ok = false;
+          } else __nanosleep(40);
         }
+      }
+    }
+  } else if (warp == kMlaCopyWarp) {
+    // ------------------- partial score tiles: this CTA's send_s[stage] -> the peer's recv_s[stage] -------------------
+    if (lane == 0) {
+      const uint32_t peer_recv = mapa_u32(smem_u32(recv_s), peer), peer_recv_full = mapa_u32(smem_u32(recv_full), peer);
+      for (int n = 0; n < nblk; ++n) {
+        const int st = n & 1, ph = (n >> 1) & 1;
+        if (!mbar_wait(&send_full[st], ph, abort_flag, a.status)) break;    // all eight warps have written their parts of block n
+        // warps 0-7 consumed the peer's block n-2 before they wrote block n: this CTA's receive stage can be armed again
+        mbar_expect_tx(&recv_full[st], kMlaXBytes);
+        bulk_copy_to_peer(peer_recv + st * kMlaXBytes, send_s + st * kMlaXBytes, kMlaXBytes, peer_recv_full + st * 8);
       }
     }
   } else if (warp >= 9) {
@@ -398,7 +436,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const int kvb = i % kMlaBufs;
       int* rows_s = ring + (i % kMlaRing) * kMlaBlk;
       if (i >= kMlaBufs) mbar_wait(&kv_free[kvb], ((i / kMlaBufs) - 1) & 1, abort_flag, a.status);
-      if (g < kMlaBlk) rows_s[g] = row_cur;
+      if (g < kMlaBlk) {
+        rows_s[g] = row_cur;
+        const uint32_t used = __ballot_sync(0xffffffffu, row_cur >= 0);       // warps 9 and 10: 32 slots each
+        if (lane == 0) masks[(i % kMlaMaskRing) * 2 + w4] = used;
+      }
       row_cur = translate(pos_nxt);                    // block i+1: for decode its table entry is requested now, used next time
       pos_nxt = load_pos(i + 2);
       named_bar_sync(2, kMlaGatherThreads);            // ids staged; every thread of the group takes the same way out of a failed wait
@@ -424,102 +466,101 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       return true;
     };
-    // Up to four blocks are in flight: the wait on kv_free inside gather() is what paces this loop.  The last buffer
-    // holds a Q panel until Q is in tensor memory.
+    // Up to four blocks are in flight: the wait on kv_free inside gather() is what paces this loop.  The last two
+    // buffers hold the Q panels until Q is in tensor memory.
     bool ok = true;
     for (int i = 0; i < nblk && ok; ++i) {
-      if (i == kMlaBufs - 1) mbar_wait(q_moved, 0, abort_flag, a.status);      // a failure shows in abort_flag inside gather()
+      if (i == kMlaBufs - 2) mbar_wait(q_moved, 0, abort_flag, a.status);      // a failure shows in abort_flag inside gather()
       ok = gather(i);
     }
-  } else if (warp >= 4) {
-    // ----------------------- exchange of the partial scores (thread = head) -----------------------
-    const int g = threadIdx.x - 128;                  // 0..127
-    const int w4 = warp - 4;
-    const uint32_t t_row = tmem + (uint32_t(w4 * 32) << 16);
-    const uint32_t peer_recv = mapa_u32(smem_u32(recv_s), peer), peer_recv_full = mapa_u32(smem_u32(recv_full), peer);
-    bool ok = __all_sync(0xffffffffu, mbar_wait(q_moved, 0, abort_flag, a.status));     // Q panels wait in the exchange buffers
-    for (int i = 0; i < nblk && ok; ++i) {
-      // partial scores of block i: tensor memory -> registers -> send_s -> the peer's recv_s
-      ok = __all_sync(0xffffffffu, mbar_wait(s_full, i & 1, abort_flag, a.status));
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t sv[kMlaBlk];
-#pragma unroll
-      for (int c = 0; c < kMlaBlk; c += 32)
-        tmem_ld32(t_row + kColS + c, *reinterpret_cast<uint32_t(*)[32]>(sv + c));
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(s_free);                             // the next block's scores may overwrite S now
-      // both softmax groups must have read the tiles of block i-1 (i = 0: both have moved Q out of the buffers)
-      ok = __all_sync(0xffffffffu, mbar_wait_cluster(xchg_free, i & 1, abort_flag, a.status));
-      if (!ok) break;
-      if (g == 0) mbar_expect_tx(recv_full, kMlaXBytes);
-#pragma unroll
-      for (int c = 0; c < 16; ++c)
-        *reinterpret_cast<uint4*>(send_s + xchg_off(g, c)) = make_uint4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
-      fence_async_smem();                              // the bulk copy reads send_s through the async proxy
-      mbar_arrive(send_full);
-      if (g == 0) {
-        ok = mbar_wait(send_full, i & 1, abort_flag, a.status);
-        if (ok) bulk_copy_to_peer(peer_recv, send_s, kMlaXBytes, peer_recv_full);
-      }
-      ok = __all_sync(0xffffffffu, ok);
-    }
   } else {
-    // ------------------------- softmax and output (thread = head) -------------------------
-    const int row = threadIdx.x;                       // 0..127 = TMEM lane
-    const uint32_t t_row = tmem + (uint32_t(warp * 32) << 16);
-    const uint32_t peer_xchg_free = mapa_u32(smem_u32(xchg_free), peer);
-    float m = -CUDART_INF_F, l = 0.f;
+    // ------------- partial-score exchange, softmax and output: thread = (head, half of a block's keys) -------------
+    const int qd = warp & 3, half = warp >> 2;
+    const int row = qd * 32 + lane;                    // head = TMEM lane
+    const uint32_t t_row = tmem + (uint32_t(qd * 32) << 16);
+    const uint32_t peer_xchg_free = mapa_u32(smem_u32(xchg_free), peer);      // [2], 8 bytes apart
+    uint16_t* max_s = reinterpret_cast<uint16_t*>(pair_s);                    // [2 buffers][2 halves][128 heads] bf16 bits
+    float m = -CUDART_INF_F, l = 0.f;                  // l: this thread's keys only
     bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, abort_flag, a.status));
     if (ok) {
-      // this head's row of the five Q panels: swizzled shared memory -> packed bf16 pairs in tensor memory
+      // this head's row of the five Q panels, swizzled shared memory -> packed bf16 pairs in tensor memory: the ten
+      // half-panels (64 B) alternate between the two threads of the head
 #pragma unroll 1
-      for (int lp = 0; lp < kMlaPanels; ++lp) {
-        uint32_t qv[32];
-        const uint8_t* src = q_stage(lp) + row * 128;
+      for (int hp = half; hp < 2 * kMlaPanels; hp += 2) {
+        uint32_t qv[16];
+        const uint8_t* src = q_stage(hp >> 1) + row * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 w = *reinterpret_cast<const uint4*>(src + ((c ^ (row & 7)) << 4));
+        for (int c = 0; c < 4; ++c) {
+          const uint4 w = *reinterpret_cast<const uint4*>(src + ((((hp & 1) * 4 + c) ^ (row & 7)) << 4));
           qv[4 * c + 0] = w.x; qv[4 * c + 1] = w.y; qv[4 * c + 2] = w.z; qv[4 * c + 3] = w.w;
         }
-        tmem_st32(t_row + kColQ + lp * 32, qv);
+        tmem_st16(t_row + kColQ + hp * 16, qv);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(q_moved);
-      __syncwarp();
-      if (lane == 0) {                                 // phase 0 of xchg_free: the staging areas of both CTAs are free
-        mbar_arrive(xchg_free);
-        mbar_arrive_remote_relaxed(peer_xchg_free);
-      }
     }
-    for (int j = 0; j < nblk && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(send_full, j & 1, abort_flag, a.status) &&
-                                       mbar_wait_cluster(recv_full, j & 1, abort_flag, a.status));
-      if (!ok) break;
-      float s[kMlaBlk];                                // raw scores; the (positive) scale is folded into the exponent's FMA
+    for (int n = 0; n <= nblk && ok; ++n) {
+      if (n < nblk) {
+        // ---- partial scores of block n: tensor memory -> registers -> fp16 in send_s[stage]; the copy warp takes it from there
+        const int st = n & 1, ph = (n >> 1) & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(s_full, n & 1, abort_flag, a.status));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sv[32];
+        tmem_ld32(t_row + kColS + 32 * half, sv);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(s_free);                           // the next block's scores may overwrite S now
+        // the peer must have read block n-2, the last user of this stage (which also means that that copy is complete)
+        if (n >= kMlaXStages) ok = __all_sync(0xffffffffu, mbar_wait(&xchg_free[st], ph ^ 1, abort_flag, a.status));
+        if (!ok) break;
+        uint8_t* send = send_s + st * kMlaXBytes;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const int off = xchg_off(row, c);
-        const float4 mine = *reinterpret_cast<const float4*>(send_s + off);
-        const float4 theirs = *reinterpret_cast<const float4*>(recv_s + off);
-        s[4 * c + 0] = mine.x + theirs.x; s[4 * c + 1] = mine.y + theirs.y;
-        s[4 * c + 2] = mine.z + theirs.z; s[4 * c + 3] = mine.w + theirs.w;
+        for (int c = 0; c < 4; ++c) {
+          auto h2 = [&](int k) { return pack_f16x2(__uint_as_float(sv[8 * c + 2 * k]), __uint_as_float(sv[8 * c + 2 * k + 1])); };
+          *reinterpret_cast<uint4*>(send + xchg_off(half, row, c)) = make_uint4(h2(0), h2(1), h2(2), h2(3));
+        }
+        fence_async_smem();                            // the bulk copy reads the tile through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&send_full[st]);
+      }
+      if (n > 0) {
+      // ---- softmax of block j = n-1: its peer tile travelled while the scores of block n were computed
+      const int j = n - 1, st = j & 1, ph = (j >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&recv_full[st], ph, abort_flag, a.status));
+      if (!ok) break;
+      float s[32];                                     // raw scores; the (positive) scale is folded into the exponent's FMA
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int off = st * kMlaXBytes + xchg_off(half, row, c);
+        const uint4 mine = *reinterpret_cast<const uint4*>(send_s + off);       // what this thread wrote itself
+        const uint4 theirs = *reinterpret_cast<const uint4*>(recv_s + off);
+        const uint32_t mw[4] = {mine.x, mine.y, mine.z, mine.w}, tw[4] = {theirs.x, theirs.y, theirs.z, theirs.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = add_f16x2_f32(mw[k], tw[k]);
+          s[8 * c + 2 * k] = x.x;
+          s[8 * c + 2 * k + 1] = x.y;
+        }
       }
       __syncwarp();
-      if (lane == 0) {                                 // both tiles are in registers: the next exchange may overwrite them
-        mbar_arrive(xchg_free);
-        mbar_arrive_remote_relaxed(peer_xchg_free);
-      }
-      float bmax = -CUDART_INF_F;
-      const int* vrow = ring + (j % kMlaRing) * kMlaBlk;
+      if (lane == 0) mbar_arrive_remote_relaxed(peer_xchg_free + st * 8);      // the peer may send into this stage again
+      const uint32_t used = masks[(j % kMlaMaskRing) * 2 + half];
+      if (used != 0xffffffffu) {                       // empty slots (the tail of a short row, holes): warp-uniform
 #pragma unroll
-      for (int i = 0; i < kMlaBlk; ++i) {
-        s[i] = vrow[i] >= 0 ? s[i] : -CUDART_INF_F;
-        bmax = fmaxf(bmax, s[i]);
+        for (int i = 0; i < 32; ++i) s[i] = (used >> i) & 1u ? s[i] : -CUDART_INF_F;
       }
-      bmax *= a.scale_log2e;
+      float bm[4] = {s[0], s[1], s[2], s[3]};          // four independent chains
+#pragma unroll
+      for (int i = 4; i < 32; ++i) bm[i & 3] = fmaxf(bm[i & 3], s[i]);
+      float bmax = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
+      // the block maximum over all 64 keys: the two threads of a head exchange theirs, rounded up to bf16
+      uint16_t* mx = max_s + (j & 1) * 256;
+      const uint32_t mine_bits = bf16_bits_round_up(bmax * a.scale_log2e);
+      mx[half * 128 + row] = static_cast<uint16_t>(mine_bits);
+      named_bar_sync(3 + qd, 64);
+      bmax = fmaxf(__uint_as_float(mine_bits << 16), __uint_as_float(uint32_t(mx[(half ^ 1) * 128 + row]) << 16));
       const float m_new = fmaxf(m, bmax);
       const bool grow = m_new - m > 8.f;               // also true when m is still -inf and m_new is finite
       bool waited_pv = false;
@@ -528,13 +569,13 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (grow) m = m_new;
         l *= alpha;
         if (j > 0) {
-          // O must be quiescent: P.V of the previous block has to be complete
+          // O must be quiescent: P.V of the previous block has to be complete.  This thread scales its half of the columns.
           ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
           if (!ok) break;
           waited_pv = true;
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < kMlaDvHalf; c += 32) {
+          for (int c = half * (kMlaDvHalf / 2); c < (half + 1) * (kMlaDvHalf / 2); c += 32) {
             uint32_t ov[32];
             tmem_ld32(t_row + kColO + c, ov);
             tmem_wait_ld();
@@ -545,37 +586,41 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
       }
       const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-      uint32_t pk[kMlaBlk / 2];
-      float psum = 0.f;
+      uint32_t pk[16];
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < kMlaBlk; i += 2) {
+      for (int i = 0; i < 32; i += 2) {
         const float p0 = fast_exp2(fmaf(s[i], a.scale_log2e, -m_eff)), p1 = fast_exp2(fmaf(s[i + 1], a.scale_log2e, -m_eff));
-        psum += p0 + p1;
+        ps[(i >> 1) & 3] += p0 + p1;
         pk[i >> 1] = pack_bf16x2(p0, p1);
       }
-      l += psum;
+      l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
       if (j > 0 && !waited_pv) {                       // P is single-buffered: P.V of the previous block must be done
         ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
         if (!ok) break;
         tc_fence_after();
       }
-#pragma unroll
-      for (int c = 0; c < kMlaBlk / 2; c += 16)
-        tmem_st16(t_row + kColP + c, *reinterpret_cast<uint32_t(*)[16]>(pk + c));
+      tmem_st16(t_row + kColP + 16 * half, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
+      }
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
     if (ok) {
       tc_fence_after();
+      // the row sum over all keys: the two threads of a head add theirs (the maxima buffer is free: every P has been consumed)
+      float* sum_s = reinterpret_cast<float*>(pair_s);
+      sum_s[half * 128 + row] = l;
+      named_bar_sync(3 + qd, 64);
+      l += sum_s[(half ^ 1) * 128 + row];
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = a.out + ((int64_t)t * a.H + hg * 128 + row) * kMlaDv + cta * kMlaDvHalf;
       const int64_t prow = (int64_t)unit * a.H + hg * 128 + row;
-      if (a.n_split > 1 && cta == 0 && row < heads_here)
+      if (a.n_split > 1 && cta == 0 && half == 0 && row < heads_here)
         a.part_lse[prow] = l > 0.f ? m + log2f(l) : -CUDART_INF_F;
 #pragma unroll 1
-      for (int c = 0; c < kMlaDvHalf; c += 32) {
+      for (int c = half * (kMlaDvHalf / 2); c < (half + 1) * (kMlaDvHalf / 2); c += 32) {
         uint32_t ov[32];
         tmem_ld32(t_row + kColO + c, ov);
         tmem_wait_ld();
