@@ -370,8 +370,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         umma_commit(s_full);
       };
       // Whatever is ready goes first: P.V of the oldest block whose P is there, else the scores of the next block (its
-      // rows gathered, S read out by warps 0-7).  Blocking on one of the two while the other could run is what used to
-      // pace the kernel: the softmax of a block ends about as late as the chain two blocks on.
+      // rows gathered, S read out by warps 0-7).  Blocking on one of the two while the other could run used to pace the
+      // kernel.  (Tried and dropped: chains first and P.V only inside a chain -- four P.V MMAs cost the pipe about 600
+      // cycles wherever they go.)
       uint32_t idle = 0;
       while (ok && pv < nblk) {
         if (pv_ready()) {
@@ -500,7 +501,48 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tc_fence_before();
       mbar_arrive(q_moved);
     }
+    // Per iteration n: first half of the softmax of block n-1 (its peer tile arrived while this warp did other things:
+    // scores, block maximum), then -- as soon as the scores of block n are complete -- their read-out and hand-over, then
+    // the second half (exponentials, P).  The read-out sits in the middle so that the first half fills the time this warp
+    // would otherwise wait for the chain, and P of block n-1 is ready early enough to be queued right behind chain n+1.
+    float s[32];                                       // raw scores of block n-1; the (positive) scale is folded into the exponent's FMA
+    float bmax = 0.f;                                  // block maximum over all 64 keys, in log2 units
     for (int n = 0; n <= nblk && ok; ++n) {
+      const int j = n - 1;
+      if (n > 0) {
+        const int st = j & 1, ph = (j >> 1) & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(&recv_full[st], ph, abort_flag, a.status));
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int off = st * kMlaXBytes + xchg_off(half, row, c);
+          const uint4 mine = *reinterpret_cast<const uint4*>(send_s + off);       // what this thread wrote itself
+          const uint4 theirs = *reinterpret_cast<const uint4*>(recv_s + off);
+          const uint32_t mw[4] = {mine.x, mine.y, mine.z, mine.w}, tw[4] = {theirs.x, theirs.y, theirs.z, theirs.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 x = add_f16x2_f32(mw[k], tw[k]);
+            s[8 * c + 2 * k] = x.x;
+            s[8 * c + 2 * k + 1] = x.y;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote_relaxed(peer_xchg_free + st * 8);      // the peer may send into this stage again
+        const uint32_t used = masks[(j % kMlaMaskRing) * 2 + half];
+        if (used != 0xffffffffu) {                       // empty slots (the tail of a short row, holes): warp-uniform
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = (used >> i) & 1u ? s[i] : -CUDART_INF_F;
+        }
+        float bm[4] = {s[0], s[1], s[2], s[3]};          // four independent chains
+#pragma unroll
+        for (int i = 4; i < 32; ++i) bm[i & 3] = fmaxf(bm[i & 3], s[i]);
+        // the block maximum over all 64 keys: the two threads of a head exchange theirs, rounded up to bf16
+        uint16_t* mx = max_s + (j & 1) * 256;
+        const uint32_t mine_bits = bf16_bits_round_up(fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3])) * a.scale_log2e);
+        mx[half * 128 + row] = static_cast<uint16_t>(mine_bits);
+        named_bar_sync(3 + qd, 64);
+        bmax = fmaxf(__uint_as_float(mine_bits << 16), __uint_as_float(uint32_t(mx[(half ^ 1) * 128 + row]) << 16));
+      }
       if (n < nblk) {
         // ---- partial scores of block n: tensor memory -> registers -> fp16 in send_s[stage]; the copy warp takes it from there
         const int st = n & 1, ph = (n >> 1) & 1;
@@ -526,84 +568,49 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (lane == 0) mbar_arrive(&send_full[st]);
       }
       if (n > 0) {
-      // ---- softmax of block j = n-1: its peer tile travelled while the scores of block n were computed
-      const int j = n - 1, st = j & 1, ph = (j >> 1) & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&recv_full[st], ph, abort_flag, a.status));
-      if (!ok) break;
-      float s[32];                                     // raw scores; the (positive) scale is folded into the exponent's FMA
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int off = st * kMlaXBytes + xchg_off(half, row, c);
-        const uint4 mine = *reinterpret_cast<const uint4*>(send_s + off);       // what this thread wrote itself
-        const uint4 theirs = *reinterpret_cast<const uint4*>(recv_s + off);
-        const uint32_t mw[4] = {mine.x, mine.y, mine.z, mine.w}, tw[4] = {theirs.x, theirs.y, theirs.z, theirs.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 x = add_f16x2_f32(mw[k], tw[k]);
-          s[8 * c + 2 * k] = x.x;
-          s[8 * c + 2 * k + 1] = x.y;
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive_remote_relaxed(peer_xchg_free + st * 8);      // the peer may send into this stage again
-      const uint32_t used = masks[(j % kMlaMaskRing) * 2 + half];
-      if (used != 0xffffffffu) {                       // empty slots (the tail of a short row, holes): warp-uniform
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[i] = (used >> i) & 1u ? s[i] : -CUDART_INF_F;
-      }
-      float bm[4] = {s[0], s[1], s[2], s[3]};          // four independent chains
-#pragma unroll
-      for (int i = 4; i < 32; ++i) bm[i & 3] = fmaxf(bm[i & 3], s[i]);
-      float bmax = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
-      // the block maximum over all 64 keys: the two threads of a head exchange theirs, rounded up to bf16
-      uint16_t* mx = max_s + (j & 1) * 256;
-      const uint32_t mine_bits = bf16_bits_round_up(bmax * a.scale_log2e);
-      mx[half * 128 + row] = static_cast<uint16_t>(mine_bits);
-      named_bar_sync(3 + qd, 64);
-      bmax = fmaxf(__uint_as_float(mine_bits << 16), __uint_as_float(uint32_t(mx[(half ^ 1) * 128 + row]) << 16));
-      const float m_new = fmaxf(m, bmax);
-      const bool grow = m_new - m > 8.f;               // also true when m is still -inf and m_new is finite
-      bool waited_pv = false;
-      if (__any_sync(0xffffffffu, grow)) {
-        const float alpha = grow ? fast_exp2(m - m_new) : 1.f;
-        if (grow) m = m_new;
-        l *= alpha;
-        if (j > 0) {
-          // O must be quiescent: P.V of the previous block has to be complete.  This thread scales its half of the columns.
-          ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
-          if (!ok) break;
-          waited_pv = true;
-          tc_fence_after();
+        const float m_new = fmaxf(m, bmax);
+        const bool grow = m_new - m > 8.f;               // also true when m is still -inf and m_new is finite
+        bool waited_pv = false;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? fast_exp2(m - m_new) : 1.f;
+          if (grow) m = m_new;
+          l *= alpha;
+          if (j > 0) {
+            // O must be quiescent: P.V of the previous block has to be complete.  This thread scales its half of the columns.
+            ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
+            if (!ok) break;
+            waited_pv = true;
+            tc_fence_after();
 #pragma unroll 1
-          for (int c = half * (kMlaDvHalf / 2); c < (half + 1) * (kMlaDvHalf / 2); c += 32) {
-            uint32_t ov[32];
-            tmem_ld32(t_row + kColO + c, ov);
-            tmem_wait_ld();
+            for (int c = half * (kMlaDvHalf / 2); c < (half + 1) * (kMlaDvHalf / 2); c += 32) {
+              uint32_t ov[32];
+              tmem_ld32(t_row + kColO + c, ov);
+              tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st32(t_row + kColO + c, ov);
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              tmem_st32(t_row + kColO + c, ov);
+            }
           }
         }
-      }
-      const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-      uint32_t pk[16];
-      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+        const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+        uint32_t pk[16];
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float p0 = fast_exp2(fmaf(s[i], a.scale_log2e, -m_eff)), p1 = fast_exp2(fmaf(s[i + 1], a.scale_log2e, -m_eff));
-        ps[(i >> 1) & 3] += p0 + p1;
-        pk[i >> 1] = pack_bf16x2(p0, p1);
-      }
-      l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-      if (j > 0 && !waited_pv) {                       // P is single-buffered: P.V of the previous block must be done
-        ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
-        if (!ok) break;
-        tc_fence_after();
-      }
-      tmem_st16(t_row + kColP + 16 * half, pk);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(p_full);
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(s[i], a.scale_log2e, -m_eff)), p1 = fast_exp2(fmaf(s[i + 1], a.scale_log2e, -m_eff));
+          ps[(i >> 1) & 3] += p0 + p1;
+          pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        if (j > 0 && !waited_pv) {                       // P is single-buffered: P.V of the previous block must be done
+          ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status));
+          if (!ok) break;
+          tc_fence_after();
+        }
+        tmem_st16(t_row + kColP + 16 * half, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_full);
       }
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
