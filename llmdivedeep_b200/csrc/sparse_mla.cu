@@ -95,8 +95,11 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
   return r;
 }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_arrive_wait() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  cluster_arrive();
+  cluster_wait();
 }
 // Arrive on the peer's barrier to say "I have READ the tile".  Relaxed on purpose: a release at cluster scope
 // costs a memory fence of thousands of cycles per block, and nothing written by this thread has to become
@@ -252,6 +255,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const int k_lo = min(a.K, split * k_per), k_cnt = min(a.K, k_lo + k_per) - k_lo;
   const int32_t* idx_row = a.idx + (int64_t)t * a.K + k_lo;
   const int heads_here = min(128, a.H - hg * 128);
+  // the five Q panels wait in the last two KV buffers for their move into tensor memory
+  auto q_stage = [&](int lp) -> uint8_t* { return kv_s + (kMlaBufs - 2) * kMlaKBytes + lp * kMlaQPanelBytes; };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -273,7 +278,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     *abort_flag = 0;
     *last_s = -1;
     mbar_fence_init();
-    tma_prefetch_desc(&tmap_q);
+    // Q is on its way before anything else happens: into this CTA's own shared memory, counted on its own barrier
+    mbar_expect_tx(q_full, kMlaPanels * kMlaQPanelBytes);
+    for (int lp = 0; lp < kMlaPanels; ++lp)          // x in 4-byte units: 32 per panel
+      tma_load_2d(q_stage(lp), &tmap_q, (lp < 4 ? cta * 4 + lp : 8) * 32, t * a.H + hg * 128, q_full);
     if constexpr (!FP8_PAGED) tma_prefetch_desc(&tmap_kv);
   }
   __syncthreads();
@@ -302,6 +310,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     // an index that is out of range is still reported
     for (int j = threadIdx.x; j < k_cnt; j += kMlaThreads)
       if (idx_row[j] >= a.S_kv && a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+    if (threadIdx.x == 0) mbar_wait(q_full, 0, abort_flag, a.status);     // the Q copy must have landed before the CTA goes
     return;
   }
   if (warp == 8) {
@@ -312,10 +321,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  cluster_arrive_wait();          // the peer's barriers are initialised before anything is sent to it
-
-  // the five Q panels wait in the last two KV buffers for their move into tensor memory
-  auto q_stage = [&](int lp) -> uint8_t* { return kv_s + (kMlaBufs - 2) * kMlaKBytes + lp * kMlaQPanelBytes; };
+  // The peer's barriers must be initialised before anything is sent to it.  Every thread arrives here; the warps that
+  // talk to the peer (0-7, copy) wait before their first remote access, the others only before they leave, so that the
+  // round trip through the cluster barrier is off the path to the first MMA.
+  cluster_arrive();
 
   if (warp == 8) {
     // ------------------------------- MMA issuer -------------------------------
@@ -324,9 +333,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(1, 1, 0, 0, 128, kMlaBlk);
       constexpr uint32_t idesc_pv = umma_idesc(1, 1, 0, 1, 128, kMlaDvHalf);
-      mbar_expect_tx(q_full, kMlaPanels * kMlaQPanelBytes);
-      for (int lp = 0; lp < kMlaPanels; ++lp)        // x in 4-byte units: 32 per panel
-        tma_load_2d(q_stage(lp), &tmap_q, (lp < 4 ? cta * 4 + lp : 8) * 32, t * a.H + hg * 128, q_full);
       bool ok = mbar_wait(q_moved, 0, abort_flag, a.status);
       uint64_t kdesc[kMlaBufs], vdesc[kMlaBufs];
 #pragma unroll
@@ -395,6 +401,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
   } else if (warp == kMlaCopyWarp) {
     // ------------------- partial score tiles: this CTA's send_s[stage] -> the peer's recv_s[stage] -------------------
+    cluster_wait();
     if (lane == 0) {
       const uint32_t peer_recv = mapa_u32(smem_u32(recv_s), peer), peer_recv_full = mapa_u32(smem_u32(recv_full), peer);
       for (int n = 0; n < nblk; ++n) {
@@ -501,6 +508,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tc_fence_before();
       mbar_arrive(q_moved);
     }
+    cluster_wait();
     // Per iteration n: first half of the softmax of block n-1 (its peer tile arrived while this warp did other things:
     // scores, block maximum), then -- as soon as the scores of block n are complete -- their read-out and hand-over, then
     // the second half (exponentials, P).  The read-out sits in the middle so that the first half fills the time this warp
@@ -652,6 +660,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
   }
 
+  __syncwarp();
+  if (warp >= 8 && warp != kMlaCopyWarp) cluster_wait();      // MMA and gather warps: the wait that pairs with the arrive above
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {
