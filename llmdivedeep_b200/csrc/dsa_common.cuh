@@ -235,5 +235,18 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
+// the same barrier, returning the OR of `flag` over its threads: one answer for all of them
+__device__ __forceinline__ bool named_bar_or(int id, int count, bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, %2, %3, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(flag)), "r"(id), "r"(count)
+      : "memory");
+  return r != 0;
+}
 
 }  // namespace dsa

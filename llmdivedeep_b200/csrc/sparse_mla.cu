@@ -9,7 +9,9 @@
 // pair owns latent panels 4c..4c+3 -- its half of V -- and half of the rope panel's contraction:
 //   * it gathers only those five panels of every selected row (40 KB per 64-key block instead of
 //     72 KB, four blocks in flight): TMA tile::gather4 from the bf16 KV, or -- for the paged FP8
-//     latent cache of decode -- 16-byte loads, e4m3 -> bf16 with the per-128 group scale;
+//     latent cache of decode -- cp.async of the raw rows into two shared-memory stages, two blocks
+//     ahead, and a shared -> shared conversion e4m3 x group scale -> bf16 (three KV buffers; the
+//     fourth one's space holds the raw stages);
 //   * its five Q panels live in tensor memory as the A operand, so Q.K^T reads no shared memory for
 //     Q, and it computes a PARTIAL score tile S_c = Q_c K_c^T (18 tcgen05.mma kind::f16 of N = 64
 //     instead of 36: back-to-back MMAs into one accumulator complete ~130 cycles apart whatever
@@ -36,6 +38,7 @@
 // Every wait is bounded (dsa_common.cuh); the two CTAs leave together through a cluster barrier.
 #include <cuda.h>
 #include <cudaTypedefs.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <math_constants.h>
 
@@ -161,62 +164,45 @@ __device__ __forceinline__ uint32_t bf16_bits_round_up(float x) {
   return ((b >> 31) || (b & 0x7fffffffu) >= 0x7f800000u) ? (b >> 16) : ((b + 0xffffu) >> 16);
 }
 
-// Paged FP8 latent cache: dequantise this CTA's panels of one block into a KV buffer.  Thread g of kMlaGatherThreads.
-// rows_s: physical cache row per slot, -1 = empty.
-__device__ __forceinline__ void dequant_block(const MlaArgs& a, const int* __restrict__ rows_s, uint8_t* kv_s, int g, int cta) {
-  constexpr int kRope = kMlaBlk * 8 / kMlaGatherThreads;          // rope chunks per thread
-  uint4 rope[kRope];
-#pragma unroll
-  for (int u = 0; u < kRope; ++u) {
-    const int q = g + u * kMlaGatherThreads;
-    const int row = rows_s[q >> 3];
-    rope[u] = make_uint4(0, 0, 0, 0);
-    if (row >= 0) rope[u] = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)row * kLatentTokenBytes + kMlaDv + 16) + (q & 7));
-  }
-  constexpr int kLat = kMlaBlk * 16 / kMlaGatherThreads;          // latent chunks (16 e4m3 values) per thread: this CTA's 256 dims
-  uint4 raw[kLat];
-  float sc[kLat];
-#pragma unroll
-  for (int u = 0; u < kLat; ++u) {
-    const int q = g + u * kMlaGatherThreads;
-    const int r = q >> 4, cc = q & 15;              // cc: 16-value chunk inside this CTA's 256 latent dims
-    const int row = rows_s[r];
-    raw[u] = make_uint4(0, 0, 0, 0);
-    sc[u] = 0.f;
-    if (row >= 0) {
-      const uint8_t* rec = a.cache + (int64_t)row * kLatentTokenBytes;
-      raw[u] = __ldg(reinterpret_cast<const uint4*>(rec + cta * kMlaDvHalf + cc * 16));
-      sc[u] = __ldg(reinterpret_cast<const float*>(rec + kMlaDv) + cta * 2 + (cc >> 3));
-    }
-  }
+// ---- paged FP8 latent cache (decode) ------------------------------------------------------------
+// A block's rows travel global -> shared memory as raw bytes with cp.async (asynchronous, two blocks ahead, no registers
+// held), and are converted shared -> shared.  A raw row is this CTA's 256 e4m3 values followed by the row's four scales.
+constexpr int kRawRow = kMlaDvHalf + 16;
+constexpr int kRawStage = kMlaBlk * kRawRow;         // 17408 bytes
+static_assert(2 * kRawStage <= kMlaKBytes, "the two raw stages take the place of the fourth KV buffer");
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, int src_bytes) {      // src_bytes 0: zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// e4m3 -> bf16 with the per-128 group scale, raw stage -> this CTA's four latent panels of a KV buffer.  Thread g of
+// kMlaGatherThreads; an empty slot was zero-filled (values and scales), so it converts to zeros.  (Tried and dropped:
+// decode's latent MMAs in fp16, so that e4m3 x scale is one conversion and one packed multiply per two values -- a third
+// of the instructions, and 9 % slower end to end: the conversion is not what paces the decode kernel.)
+__device__ __forceinline__ void convert_block(const uint8_t* stage, uint8_t* kv_s, int g, int cta) {
+  constexpr int kLat = kMlaBlk * 16 / kMlaGatherThreads;          // 16-value chunks per thread
 #pragma unroll
   for (int u = 0; u < kLat; ++u) {
     const int q = g + u * kMlaGatherThreads;
-    const int r = q >> 4, cc = q & 15;
-    const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+    const int r = q >> 4, cc = q & 15;              // row, chunk inside this CTA's 256 latent dims
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + r * kRawRow + cc * 16);
+    const float sc = *reinterpret_cast<const float*>(stage + r * kRawRow + kMlaDvHalf + (cta * 2 + (cc >> 3)) * 4);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     uint32_t outw[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const __nv_fp8x2_storage_t pr = static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * hh)) & 0xffffu);
-        const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3);
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-        outw[i * 2 + hh] = pack_bf16x2(f.x * sc[u], f.y * sc[u]);
-      }
+    for (int i = 0; i < 8; ++i) {
+      const __nv_fp8x2_storage_t pr = static_cast<__nv_fp8x2_storage_t>((w[i >> 1] >> (16 * (i & 1))) & 0xffffu);
+      const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+      outw[i] = pack_bf16x2(f.x * sc, f.y * sc);
     }
     const int p = cc >> 2, c = (cc & 3) * 2;        // local panel, 16-byte chunk inside the 128-byte row (even)
     uint8_t* base = kv_s + p * kMlaKPanelBytes + r * 128;
     *reinterpret_cast<uint4*>(base + ((c ^ (r & 7)) << 4)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
     *reinterpret_cast<uint4*>(base + (((c + 1) ^ (r & 7)) << 4)) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
   }
-#pragma unroll
-  for (int u = 0; u < kRope; ++u) {
-    const int q = g + u * kMlaGatherThreads;
-    const int r = q >> 3, c = q & 7;
-    *reinterpret_cast<uint4*>(kv_s + 4 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = rope[u];
-  }
-  fence_async_smem();          // make the panel writes visible to the tensor core's reads
 }
 
 template <bool FP8_PAGED>
@@ -224,6 +210,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaThreads, 1)
 sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int NB = FP8_PAGED ? kMlaBufs - 1 : kMlaBufs;      // KV buffers in use (decode: the fourth holds the raw stages)
   uint8_t* kv_s = smem;                                        // four buffers x five panels [64 keys x 128 B]
   uint8_t* send_s = kv_s + kMlaBufs * kMlaKBytes;              // [2] this CTA's partial score tiles
   uint8_t* recv_s = send_s + kMlaXStages * kMlaXBytes;         // [2] the peer's
@@ -256,7 +243,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const int32_t* idx_row = a.idx + (int64_t)t * a.K + k_lo;
   const int heads_here = min(128, a.H - hg * 128);
   // the five Q panels wait in the last two KV buffers for their move into tensor memory
-  auto q_stage = [&](int lp) -> uint8_t* { return kv_s + (kMlaBufs - 2) * kMlaKBytes + lp * kMlaQPanelBytes; };
+  auto q_stage = [&](int lp) -> uint8_t* { return kv_s + (NB - 2) * kMlaKBytes + lp * kMlaQPanelBytes; };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -345,11 +332,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // P.V of block j: four MMAs (N = 256) and the commits that release the block's KV buffer, P and O
       auto pv_mmas = [&](int j) {
         tc_fence_after();
-        const uint64_t vd = pick(vdesc, j % kMlaBufs);
+        const uint64_t vd = pick(vdesc, j % NB);
 #pragma unroll
         for (int ks = 0; ks < kMlaBlk / 16; ++ks)     // 16 keys per step: 16 rows x 128 B further into each panel
           umma_f16_ts(tmem + kColO, tmem + kColP + 8 * ks, vd + ks * (2048 >> 4), idesc_pv, (j | ks) != 0);
-        umma_commit(&kv_free[j % kMlaBufs]);
+        umma_commit(&kv_free[j % NB]);
         umma_commit(pv_done);
         if (j == nblk - 1) umma_commit(o_final);
       };
@@ -360,7 +347,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       auto pv_ready = [&]() { return pv < qk && mbar_try_wait(p_full, pv & 1); };
       auto issue_qk = [&](int i) {
         tc_fence_after();
-        const uint64_t kd0 = pick(kdesc, i % kMlaBufs);
+        const uint64_t kd0 = pick(kdesc, i % NB);
 #pragma unroll
         for (int lp = 0; lp < 4; ++lp) {
 #pragma unroll
@@ -384,7 +371,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (pv_ready()) {
           pv_mmas(pv++);
           idle = 0;
-        } else if (qk < nblk && mbar_try_wait(&kv_full[qk % kMlaBufs], (qk / kMlaBufs) & 1) &&
+        } else if (qk < nblk && mbar_try_wait(&kv_full[qk % NB], (qk / NB) & 1) &&
                    (qk == 0 || mbar_try_wait(s_free, (qk - 1) & 1))) {
           issue_qk(qk);
           ++qk;
@@ -438,26 +425,24 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         return -1;
       }
     };
-    int row_cur = translate(load_pos(0)), pos_nxt = load_pos(1);
-    // stage the row ids of block i and fill its KV buffer; called for i = 0, 1, 2, ... in order
-    auto gather = [&](int i) -> bool {
-      const int kvb = i % kMlaBufs;
-      int* rows_s = ring + (i % kMlaRing) * kMlaBlk;
-      if (i >= kMlaBufs) mbar_wait(&kv_free[kvb], ((i / kMlaBufs) - 1) & 1, abort_flag, a.status);
-      if (g < kMlaBlk) {
-        rows_s[g] = row_cur;
-        const uint32_t used = __ballot_sync(0xffffffffu, row_cur >= 0);       // warps 9 and 10: 32 slots each
-        if (lane == 0) masks[(i % kMlaMaskRing) * 2 + w4] = used;
-      }
-      row_cur = translate(pos_nxt);                    // block i+1: for decode its table entry is requested now, used next time
-      pos_nxt = load_pos(i + 2);
-      named_bar_sync(2, kMlaGatherThreads);            // ids staged; every thread of the group takes the same way out of a failed wait
-      if (*abort_flag) return false;
-      uint8_t* dst = kv_s + kvb * kMlaKBytes;
-      if constexpr (FP8_PAGED) {
-        dequant_block(a, rows_s, dst, g, cta);
-        mbar_arrive(&kv_full[kvb]);
-      } else {
+    bool ok = true;
+    if constexpr (!FP8_PAGED) {
+      int row_cur = translate(load_pos(0)), pos_nxt = load_pos(1);
+      // stage the row ids of block i and fill its KV buffer; called for i = 0, 1, 2, ... in order
+      auto gather = [&](int i) -> bool {
+        const int kvb = i % NB;
+        int* rows_s = ring + (i % kMlaRing) * kMlaBlk;
+        if (i >= NB) mbar_wait(&kv_free[kvb], ((i / NB) - 1) & 1, abort_flag, a.status);
+        if (g < kMlaBlk) {
+          rows_s[g] = row_cur;
+          const uint32_t used = __ballot_sync(0xffffffffu, row_cur >= 0);       // warps 9 and 10: 32 slots each
+          if (lane == 0) masks[(i % kMlaMaskRing) * 2 + w4] = used;
+        }
+        row_cur = translate(pos_nxt);
+        pos_nxt = load_pos(i + 2);
+        // ids staged; every thread of the group takes the same way out of a failed wait
+        if (named_bar_or(2, kMlaGatherThreads, *abort_flag != 0)) return false;
+        uint8_t* dst = kv_s + kvb * kMlaKBytes;
         // warp w4 fetches kRowsPerWarp consecutive rows: lane = 5 * (group of four rows) + panel, one gather4 each
         constexpr int kRowsPerWarp = kMlaBlk / kMlaGatherWarps, kLanes = kRowsPerWarp / 4 * kMlaPanels;
         if (lane == 0) mbar_expect_tx(&kv_full[kvb], kLanes * 512);
@@ -471,15 +456,103 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           tma_gather4(dst + lp * kMlaKPanelBytes + r0 * 128, &tmap_kv, x, rid(r0), rid(r0 + 1), rid(r0 + 2), rid(r0 + 3),
                       &kv_full[kvb]);
         }
+        return true;
+      };
+      // Up to four blocks are in flight: the wait on kv_free inside gather() is what paces this loop.  The last two
+      // buffers hold the Q panels until Q is in tensor memory.
+      for (int i = 0; i < nblk && ok; ++i) {
+        if (i == NB - 2) mbar_wait(q_moved, 0, abort_flag, a.status);      // a failure shows in abort_flag inside gather()
+        ok = gather(i);
       }
-      return true;
-    };
-    // Up to four blocks are in flight: the wait on kv_free inside gather() is what paces this loop.  The last two
-    // buffers hold the Q panels until Q is in tensor memory.
-    bool ok = true;
-    for (int i = 0; i < nblk && ok; ++i) {
-      if (i == kMlaBufs - 2) mbar_wait(q_moved, 0, abort_flag, a.status);      // a failure shows in abort_flag inside gather()
-      ok = gather(i);
+    } else {
+      // Decode.  Block b's raw rows are requested two blocks ahead with cp.async into one of two raw stages (the space of
+      // the fourth KV buffer), its rope halves with plain loads into registers; block b is converted into its KV buffer
+      // while blocks b+1 and b+2 are on their way.  The page-table entry of a slot is requested one call before it is
+      // examined, its position one call before that, so that no global-memory latency sits in the loop.
+      uint8_t* raw_s = kv_s + NB * kMlaKBytes;
+      auto table_entry = [&](int pos) -> int {
+        return (pos >= 0 && pos < a.S_kv) ? __ldg(a.block_table + (int64_t)t * a.table_stride + pos / kLatentPage) : -1;
+      };
+      auto cache_row = [&](int pos, int phys) -> int {   // -1 = empty slot; bad positions and page ids are flagged and skipped
+        if (pos < 0) return -1;
+        if (pos < a.S_kv && phys >= 0 && (int64_t)(phys + 1) * kLatentPage <= a.num_phys_rows)
+          return phys * kLatentPage + pos % kLatentPage;
+        if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
+        return -1;
+      };
+      uint4 rope_e[2], rope_o[2];                      // rope chunks of the even / odd block in flight
+      // request block b: stage its row ids (and the validity mask for the softmax), then issue the copies
+      auto fetch = [&](int b, int row, uint4 (&rope)[2]) {
+        int* rows_s = ring + (b & 1) * kMlaBlk;
+        if (g < kMlaBlk) {
+          rows_s[g] = row;
+          const uint32_t used = __ballot_sync(0xffffffffu, row >= 0);            // warps 9 and 10: 32 slots each
+          if (lane == 0) masks[(b % kMlaMaskRing) * 2 + w4] = used;
+        }
+        named_bar_sync(2, kMlaGatherThreads);            // ids staged; everyone is done with the raw stage that is overwritten next
+        if (b < nblk) {
+          uint8_t* stage = raw_s + (b & 1) * kRawStage;
+          constexpr int kCopies = kMlaBlk * 17;          // 16 value chunks + the scales, per row
+#pragma unroll
+          for (int u = 0; u < (kCopies + kMlaGatherThreads - 1) / kMlaGatherThreads; ++u) {
+            const int q = g + u * kMlaGatherThreads;
+            if (q < kCopies) {
+              const int r = q / 17, c = q - r * 17;
+              const int rr = rows_s[r];
+              const uint8_t* rec = a.cache + (int64_t)(rr >= 0 ? rr : 0) * kLatentTokenBytes;
+              cp_async_16(stage + r * kRawRow + c * 16, rec + (c < 16 ? cta * kMlaDvHalf + c * 16 : kMlaDv), rr >= 0 ? 16 : 0);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {                  // this CTA's two K-steps of the rope panel: 64 bytes per row
+            const int q = g + u * kMlaGatherThreads;
+            const int rr = rows_s[q >> 2];
+            rope[u] = make_uint4(0, 0, 0, 0);
+            if (rr >= 0)
+              rope[u] = __ldg(reinterpret_cast<const uint4*>(a.cache + (int64_t)rr * kLatentTokenBytes + kMlaDv + 16) + cta * 4 + (q & 3));
+          }
+        }
+        cp_async_commit();                               // one group per call, empty or not: the counting below relies on it
+      };
+      int P2, T2, P3;                                    // position / table entry of this thread's slot in block i+2, position in block i+3
+      {
+        const int p0 = load_pos(0), p1 = load_pos(1);
+        P2 = load_pos(2);
+        P3 = load_pos(3);
+        const int t0 = table_entry(p0), t1 = table_entry(p1);
+        T2 = table_entry(P2);
+        fetch(0, cache_row(p0, t0), rope_e);
+        fetch(1, cache_row(p1, t1), rope_o);
+      }
+      auto step = [&](int i, uint4 (&rope)[2]) -> bool {
+        const int kvb = i % NB;
+        if (i == NB - 2) mbar_wait(q_moved, 0, abort_flag, a.status);    // buffers NB-2 and NB-1 held the Q panels
+        if (i >= NB) mbar_wait(&kv_free[kvb], ((i / NB) - 1) & 1, abort_flag, a.status);
+        cp_async_wait<1>();                              // this thread's copies of block i have landed (block i+1 may be in flight)
+        // ... and everyone else's; every thread of the group takes the same way out of a failed wait
+        if (named_bar_or(2, kMlaGatherThreads, *abort_flag != 0)) return false;
+        uint8_t* dst = kv_s + kvb * kMlaKBytes;
+        convert_block(raw_s + (i & 1) * kRawStage, dst, g, cta);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int q = g + u * kMlaGatherThreads;
+          const int r = q >> 2, c = cta * 4 + (q & 3);
+          *reinterpret_cast<uint4*>(dst + 4 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = rope[u];
+        }
+        fence_async_smem();                              // make the panel writes visible to the tensor core's reads
+        mbar_arrive(&kv_full[kvb]);
+        const int row = cache_row(P2, T2);               // block i+2
+        P2 = P3;
+        T2 = table_entry(P2);
+        P3 = load_pos(i + 4);
+        fetch(i + 2, row, rope);
+        return true;
+      };
+      for (int i = 0; i < nblk && ok; i += 2) {
+        ok = step(i, rope_e);
+        if (ok && i + 1 < nblk) ok = step(i + 1, rope_o);
+      }
+      cp_async_wait<0>();                                // nothing of this thread's is in flight into shared memory when it leaves
     }
   } else {
     // ------------- partial-score exchange, softmax and output: thread = (head, half of a block's keys) -------------
