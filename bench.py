@@ -626,6 +626,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the sub-records and the incumbent comparison")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--gather", choices=("peer", "nccl"), default="peer",
+                    help="N > 1: how the ranks exchange the attention output (copies into symmetric memory, or NCCL all-gather)")
     ap.add_argument("--chunk-rows", type=int, default=0, help="query rows per pipeline chunk (default: 4096 on one GPU, 2048 on several)")
     ap.add_argument("--seq", type=int, default=S_PREFILL,
                     help="prefill length; anything but 131072 is a reduced case for profiler captures, not a bench value")
@@ -678,11 +680,27 @@ def main():
         return float(t.item())
 
     chunk_rows = args.chunk_rows or (4096 if world == 1 else 2048)
-    pipe = layer.PrefillPipeline(S, dev, n_heads=MLA_HEADS, topk=TOPK, chunk_rows=chunk_rows, softmax_scale=SCALE,
-                                 rank=rank, world=world, block_rows=BLOCK_ROWS)
+    # Output exchange between the ranks: plain copies into symmetric memory (copy engines, no SMs) unless --gather nccl;
+    # if symmetric memory cannot be set up on any rank, every rank falls back to the NCCL all-gather.
+    transport = "peer" if (world > 1 and args.gather == "peer") else "nccl"
+    pipe = out_full = None
+    while out_full is None:
+        pipe = layer.PrefillPipeline(S, dev, n_heads=MLA_HEADS, topk=TOPK, chunk_rows=chunk_rows, softmax_scale=SCALE,
+                                     rank=rank, world=world, block_rows=BLOCK_ROWS, transport=transport)
+        try:
+            out_full, made = pipe.output_buffer(), 1
+        except Exception as exc:                               # noqa: BLE001 - reported below, then the NCCL path
+            made = 0
+            print(f"rank {rank}: symmetric memory unavailable ({exc!r}); output exchange by NCCL all-gather", file=sys.stderr)
+        if world > 1:
+            agreed = torch.tensor([made], device=dev)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 0:
+                if transport == "nccl":
+                    raise RuntimeError("no output buffer could be allocated")
+                out_full, transport = None, "nccl"
     inputs = make_prefill_inputs(dev, 0, S, pipe.pos)
     q8, k8, ksc, w, q, kv = inputs
-    out_full = torch.empty(S, MLA_HEADS, 512, dtype=torch.bfloat16, device=dev)
 
     # ---- device-resident throughput -----------------------------------------------------------------
     for _ in range(args.warmup):
@@ -829,9 +847,13 @@ def main():
         "config": {"workload": workload,
                    "l2": "inputs of one step are 20 GB (MLA q 19.3 GB, indexer q 1.07 GB) and the output 17.2 GB: far larger than the 126 MB L2",
                    "chunk_rows": chunk_rows,
-                   "sharding": "one sequence; 256-row blocks of query rows dealt round-robin over the ranks, keys and latent KV "
-                               "replicated; output all-gathered per finished chunk on a side stream (NCCL), one collective per "
-                               "round of blocks straight into row order" if world > 1 else "one GPU, no collective"},
+                   "sharding": ("one sequence; 256-row blocks of query rows dealt round-robin over the ranks, keys and latent KV "
+                                "replicated; " + ("every finished block copied into every rank's output (symmetric memory) by "
+                                                  "device-to-device copies on a side stream, two 4-byte all-reduces per step"
+                                                  if pipe.transport == "peer" else
+                                                  "output all-gathered per finished chunk on a side stream (NCCL), one collective "
+                                                  "per round of blocks straight into row order")) if world > 1 else "one GPU, no collective",
+                   "output_exchange": pipe.transport if world > 1 else None},
         "gpu_launches": pipe.launches_per_run * args.steps,
         "clocks": clocks,
         "roofline": dominant,

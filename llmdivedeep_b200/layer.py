@@ -127,7 +127,13 @@ class PrefillPipeline:
     `block_rows`-row blocks round-robin (sharding.round_robin_blocks): a rank runs only its own blocks --
     keys and latent KV are replicated, nothing is exchanged before the output -- and the attention output
     of every finished chunk is all-gathered on a side stream, one collective per round of `world` blocks
-    straight into its place in the full output, while the next chunk computes.
+    straight into its place in the full output, while the next chunk computes.  With transport="peer" there
+    is no collective kernel at all: the output lives in symmetric memory (output_buffer()), and a finished
+    block is written into every rank's copy by plain device-to-device copies on the side stream -- the copy
+    engines move it over NVLink and the SMs stay with the attention kernel, whose CTAs fill every SM's
+    shared memory so that a collective's CTAs can only run in the gaps between its waves.  Two 4-byte
+    all-reduces per run() order the ranks: one before the first copy (every rank is done with the previous
+    output), one after the last (every rank's copies have landed).
 
     Tensors given to run() hold the rank's rows in local order (for world == 1 that is the sequence
     itself): q_idx [T_loc, Hi, Di] e4m3, w [T_loc, Hi], q [T_loc, H, 576] bf16; replicated k_idx [S, Di]
@@ -136,7 +142,9 @@ class PrefillPipeline:
 
     def __init__(self, S: int, device, n_heads: int = 128, topk: int = 2048, chunk_rows: int = 4096,
                  softmax_scale: float = 192 ** -0.5, rank: int = 0, world: int = 1, block_rows: int = 256,
-                 group=None, select=None, attend=None):
+                 group=None, select=None, attend=None, transport: str = "nccl"):
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' or 'peer'")
         if chunk_rows % block_rows:
             raise ValueError("chunk_rows must be a whole number of row blocks")
         self.S, self.device, self.H, self.k = S, torch.device(device), n_heads, min(topk, S)
@@ -162,6 +170,9 @@ class PrefillPipeline:
         if select is None and self.rows_max:
             nbytes = _lib.load().dsa_indexer_topk_workspace_bytes(self.rows_max, S)
             self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.transport = transport if (world > 1 and self.cuda) else "nccl"
+        self._peers = None                             # transport "peer": every rank's output, as seen from this GPU
+        self._symm = None
         self.local = None
         if world > 1:
             self.local = [torch.empty(self.rows_max, n_heads, 512, dtype=torch.bfloat16, device=self.device)
@@ -178,11 +189,43 @@ class PrefillPipeline:
     def _attend(self, q, kv, idx, scale, out):
         return ops.sparse_mla_prefill(q, kv, idx, scale, out=out)
 
+    def output_buffer(self) -> torch.Tensor:
+        """The [S, H, 512] bf16 tensor to pass to run() as out_full.  Plain device memory, or -- transport "peer" --
+        symmetric memory mapped into every rank of the group (a collective call: every rank makes it, once)."""
+        shape = (self.S, self.H, 512)
+        if self.transport != "peer":
+            return torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        out = symm.empty(*shape, dtype=torch.bfloat16, device=self.device)
+        handle = symm.rendezvous(out, self.group if self.group is not None else dist.group.WORLD)
+        self._peers = [handle.get_buffer(r, shape, torch.bfloat16) for r in range(self.world)]
+        self._symm = (out, handle)
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return out
+
+    def _order_ranks(self):
+        """A 4-byte all-reduce on the current stream: passes once every rank's stream has reached this point."""
+        import torch.distributed as dist
+        dist.all_reduce(self._token, group=self.group)
+
+    def begin(self, out_full):
+        """Start of one prefill: with transport "peer" no rank may write into another's output before that rank is done
+        with the previous one (everything it enqueued on its stream before this call)."""
+        if self.transport == "peer":
+            if self._symm is None or out_full.data_ptr() != self._symm[0].data_ptr():
+                raise ValueError('transport "peer" writes into the tensor output_buffer() returned')
+            self._order_ranks()
+
     def _gather_chunk(self, out_full, local, b0, b1):
         off = 0
         for j in range(b0, b1):
             a, e = self.blocks[j]
-            sharding.all_gather_round(out_full, local[off:off + (e - a)], j, self.S, self.world, self.block, self.group)
+            if self.transport == "peer":
+                for peer in self._peers:               # own copy included; contiguous rows: one memcpy each
+                    peer[a:e].copy_(local[off:off + (e - a)], non_blocking=True)
+            else:
+                sharding.all_gather_round(out_full, local[off:off + (e - a)], j, self.S, self.world, self.block, self.group)
             off += e - a
 
     @torch.no_grad()
@@ -217,14 +260,18 @@ class PrefillPipeline:
 
     @torch.no_grad()
     def run(self, q_idx, k_idx, k_scale, w, q, kv, out_full):
+        self.begin(out_full)
         for c, (a, b, _, _) in enumerate(self.chunks):
             self.run_chunk(c, q_idx[a:b], k_idx, k_scale, w[a:b], q[a:b], kv, out_full)
         self.finish()
         return out_full
 
     def finish(self):
-        """The current stream waits for the output collectives issued so far."""
+        """The current stream waits for the output collectives (copies: of every rank) issued so far."""
         if self.world > 1 and self.cuda:
+            if self.transport == "peer":
+                with torch.cuda.stream(self.comm):
+                    self._order_ranks()                # behind this rank's copies; passes when every rank's have landed
             torch.cuda.current_stream(self.device).wait_stream(self.comm)
 
 
@@ -264,6 +311,7 @@ class HostPrefillPipeline:
             self._first = False
         n = len(p.chunks)
         ready = [torch.cuda.Event() for _ in range(n)]
+        p.begin(out_full)
 
         def stage(c):
             a, b, _, _ = p.chunks[c]

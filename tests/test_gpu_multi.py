@@ -65,19 +65,26 @@ def _pipeline_worker(rank, world, port, q_out):
         g = torch.Generator().manual_seed(51)
         q = torch.randn(S, H, 576, generator=g).to(torch.bfloat16).to(dev)
         kv = torch.randn(S, 576, generator=g).to(torch.bfloat16).to(dev)
-        pipe = layer.PrefillPipeline(S, dev, n_heads=H, topk=K, chunk_rows=512, softmax_scale=0.05, rank=rank, world=world)
-        rows = pipe.pos.long()
-        out = torch.zeros(S, H, 512, dtype=torch.bfloat16, device=dev)
-        for _ in range(2):                                      # twice: buffers and events are reused across runs
-            pipe.run(q8.view(torch.uint8)[rows].view(q8.dtype), k8, ksc, w[rows], q[rows], kv, out)
-        torch.cuda.synchronize()
-        ops.check_status(dev)
-        if rank == 0:
-            one = layer.PrefillPipeline(S, dev, n_heads=H, topk=K, chunk_rows=1024, softmax_scale=0.05)
-            want = one.run(q8, k8, ksc, w, q, kv, torch.zeros_like(out))
+        same = []
+        for transport in ("nccl", "peer"):                      # NCCL all-gather; copies into symmetric memory
+            pipe = layer.PrefillPipeline(S, dev, n_heads=H, topk=K, chunk_rows=512, softmax_scale=0.05, rank=rank, world=world,
+                                         transport=transport)
+            rows = pipe.pos.long()
+            out = pipe.output_buffer()
+            for _ in range(2):                                  # twice: buffers and events are reused across runs
+                out.zero_()
+                pipe.run(q8.view(torch.uint8)[rows].view(q8.dtype), k8, ksc, w[rows], q[rows], kv, out)
             torch.cuda.synchronize()
-            q_out.put((bool(torch.equal(pipe.idx, one.idx[rows])), bool(torch.equal(out, want))))
-        dist.barrier()
+            ops.check_status(dev)
+            dist.barrier()
+            if rank == 0:
+                one = layer.PrefillPipeline(S, dev, n_heads=H, topk=K, chunk_rows=1024, softmax_scale=0.05)
+                want = one.run(q8, k8, ksc, w, q, kv, torch.zeros_like(out))
+                torch.cuda.synchronize()
+                same += [bool(torch.equal(pipe.idx, one.idx[rows])), bool(torch.equal(out, want))]
+            dist.barrier()
+        if rank == 0:
+            q_out.put((same[0] and same[2], same[1] and same[3]))
     finally:
         dist.destroy_process_group()
 
