@@ -121,6 +121,25 @@ def test_decode_paged_matches_oracle(B, H, P, K):
     check(out, O.sparse_mla_decode_paged(q.float(), cache, table, idx, 0.06, round_bf16=True))
 
 
+def test_decode_holes_and_odd_block_counts():
+    """Holes inside the slot list (empty slots are zero-filled rows with a cleared validity bit) and slot lists of one,
+    three and five 64-key blocks: the gather alternates between two raw stages and two sets of rope registers."""
+    for K in (40, 130, 300):
+        g = torch.Generator().manual_seed(K)
+        B, H, P = 3, 128, 6
+        kv = torch.randn(B * P * 64, 576, generator=g).to(torch.bfloat16)
+        cache = O.pack_latent_cache(kv)
+        table = torch.randperm(B * P, generator=g).int().view(B, P)
+        idx = torch.stack([torch.randperm(P * 64, generator=g)[:K] for _ in range(B)]).int()
+        idx[0, ::3] = -1
+        idx[1, 1::2] = -1
+        idx[2, : K // 2] = -1                                  # leading blocks empty, trailing ones used
+        q = torch.randn(B, H, 576, generator=g).to(torch.bfloat16)
+        out = ops.sparse_mla_decode_paged(q.cuda(), cache.cuda(), table.cuda(), idx.cuda(), 0.06)
+        ops.check_status("cuda")
+        check(out, O.sparse_mla_decode_paged(q.float(), cache, table, idx, 0.06, round_bf16=True))
+
+
 def test_decode_bad_page_is_flagged():
     g = torch.Generator().manual_seed(2)
     kv = torch.randn(4 * 64, 576, generator=g).to(torch.bfloat16)
