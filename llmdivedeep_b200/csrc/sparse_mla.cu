@@ -90,6 +90,7 @@ struct MlaArgs {
   int n_split;                    // > 1: each query's slot list is cut into n_split parts (decode with few queries)
   float* part_o;                  // [T * n_split, H, 512] fp32 normalised partial outputs
   float* part_lse;                // [T * n_split, H] log2-sum-exp of each part (-inf = empty part)
+  int tma_out;                    // the output tensor map is valid: full 128-head groups leave through TMA stores
 };
 
 // ---- cluster helpers ----------------------------------------------------------------------------
@@ -125,6 +126,15 @@ __device__ __forceinline__ void tma_gather4(void* dst, const void* tmap, int x, 
       "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_u32(bar))
       : "memory");
+}
+
+// one [rows x 128 B] panel, shared memory (128-B swizzle) -> global, tracked by the thread's bulk group
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(src)) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_and_wait_read() {      // shared memory may be reused / released afterwards
+  asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -207,7 +217,8 @@ __device__ __forceinline__ void convert_block(const uint8_t* stage, uint8_t* kv_
 
 template <bool FP8_PAGED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaThreads, 1)
-sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv, const MlaArgs a) {
+sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
+                  const __grid_constant__ CUtensorMap tmap_o, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int NB = FP8_PAGED ? kMlaBufs - 1 : kMlaBufs;      // KV buffers in use (decode: the fourth holds the raw stages)
@@ -245,38 +256,54 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   // the five Q panels wait in the last two KV buffers for their move into tensor memory
   auto q_stage = [&](int lp) -> uint8_t* { return kv_s + (NB - 2) * kMlaKBytes + lp * kMlaQPanelBytes; };
 
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_moved, 256);
-    mbar_init(o_final, 1);
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 256);
-    mbar_init(p_full, 256);
-    mbar_init(pv_done, 1);
-    for (int st = 0; st < kMlaXStages; ++st) {
-      mbar_init(&send_full[st], 8);                  // lane 0 of warps 0-7
-      mbar_init(&recv_full[st], 1);
-      mbar_init(&xchg_free[st], 8);                  // lane 0 of the peer's warps 0-7
-    }
-    for (int b = 0; b < kMlaBufs; ++b) {
-      mbar_init(&kv_full[b], FP8_PAGED ? kMlaGatherThreads : kMlaGatherWarps);
-      mbar_init(&kv_free[b], 1);
-    }
-    *abort_flag = 0;
-    *last_s = -1;
-    mbar_fence_init();
-    // Q is on its way before anything else happens: into this CTA's own shared memory, counted on its own barrier
-    mbar_expect_tx(q_full, kMlaPanels * kMlaQPanelBytes);
-    for (int lp = 0; lp < kMlaPanels; ++lp)          // x in 4-byte units: 32 per panel
-      tma_load_2d(q_stage(lp), &tmap_q, (lp < 4 ? cta * 4 + lp : 8) * 32, t * a.H + hg * 128, q_full);
-    if constexpr (!FP8_PAGED) tma_prefetch_desc(&tmap_kv);
+  // ---- set-up, arranged so that nothing waits for anything it does not need ------------------------------------
+  // every thread requests its share of the slot list first (the scan below decides the number of key blocks) ...
+  constexpr int kScan = 8;
+  int pos[kScan];
+#pragma unroll
+  for (int u = 0; u < kScan; ++u) {
+    const int j = threadIdx.x + u * kMlaThreads;
+    pos[u] = j < k_cnt ? __ldg(idx_row + j) : -1;
   }
+  // ... while warp 0 initialises the barriers (one per lane) and sends for Q (one panel per lane) and warp 8 allocates
+  // tensor memory
+  if (warp == 0) {
+    if (lane < 21) {
+      const uint32_t count = (lane == 1 || lane == 4 || lane == 5) ? 256u           // q_moved, s_free, p_full: warps 0-7
+                             : (lane == 7 || lane == 8) ? 8u                         // send_full: lane 0 of warps 0-7
+                             : (lane == 11 || lane == 12) ? 8u                       // xchg_free: lane 0 of the peer's warps 0-7
+                             : (lane >= 13 && lane <= 16) ? (FP8_PAGED ? uint32_t(kMlaGatherThreads) : uint32_t(kMlaGatherWarps))
+                                                          : 1u;                      // q_full, o_final, s_full, pv_done, recv_full, kv_free
+      mbar_init(bars + lane, count);
+      mbar_fence_init();
+    }
+    if (lane == 0) {
+      *abort_flag = 0;
+      *last_s = -1;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_expect_tx(q_full, kMlaPanels * kMlaQPanelBytes);
+    __syncwarp();
+    // Q is on its way before anything else happens: into this CTA's own shared memory, counted on its own barrier
+    if (lane < kMlaPanels)                             // x in 4-byte units: 32 per panel
+      tma_load_2d(q_stage(lane), &tmap_q, (lane < 4 ? cta * 4 + lane : 8) * 32, t * a.H + hg * 128, q_full);
+    if (lane == kMlaPanels && !FP8_PAGED) tma_prefetch_desc(&tmap_kv);
+    if (lane == kMlaPanels + 1 && a.tma_out) tma_prefetch_desc(&tmap_o);
+  } else if (warp == 8) {
+    tmem_alloc(tmem_slot, kMlaTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
   {  // the last usable slot decides the number of key blocks (the same number in both CTAs of the pair)
     int last = -1;
-    for (int j = threadIdx.x; j < k_cnt; j += kMlaThreads) {
-      const int pos = idx_row[j];
-      if (pos >= 0 && pos < a.S_kv) last = j;
+#pragma unroll
+    for (int u = 0; u < kScan; ++u)
+      if (pos[u] >= 0 && pos[u] < a.S_kv) last = threadIdx.x + u * kMlaThreads;
+    for (int j = threadIdx.x + kScan * kMlaThreads; j < k_cnt; j += kMlaThreads) {      // slot lists beyond 3584: rare
+      const int p = idx_row[j];
+      if (p >= 0 && p < a.S_kv) last = j;
     }
     if (last >= 0) atomicMax(last_s, last);
   }
@@ -298,15 +325,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     for (int j = threadIdx.x; j < k_cnt; j += kMlaThreads)
       if (idx_row[j] >= a.S_kv && a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
     if (threadIdx.x == 0) mbar_wait(q_full, 0, abort_flag, a.status);     // the Q copy must have landed before the CTA goes
+    if (warp == 8) tmem_dealloc(*tmem_slot, kMlaTmemCols);
     return;
   }
-  if (warp == 8) {
-    tmem_alloc(tmem_slot, kMlaTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   // The peer's barriers must be initialised before anything is sent to it.  Every thread arrives here; the warps that
   // talk to the peer (0-7, copy) wait before their first remote access, the others only before they leave, so that the
@@ -695,6 +716,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
+    // A full group of 128 heads leaves through shared memory and TMA stores: four [128 heads x 128 B] panels in the
+    // (now idle) first two KV buffers, written asynchronously in whole lines.  16-byte stores from the threads -- every
+    // lane its own 1 KB-strided row -- cost about 4 % of the kernel.
+    const bool by_tma = a.tma_out && a.n_split == 1 && heads_here == 128;
     if (ok) {
       tc_fence_after();
       // the row sum over all keys: the two threads of a head add theirs (the maxima buffer is free: every P has been consumed)
@@ -712,7 +737,19 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         uint32_t ov[32];
         tmem_ld32(t_row + kColO + c, ov);
         tmem_wait_ld();
-        if (row < heads_here && a.n_split > 1) {
+        if (by_tma) {
+          uint8_t* prow_s = kv_s + (c >> 6) * kMlaQPanelBytes + row * 128;
+          const int ch0 = (c & 63) >> 3;                 // first of this iteration's four 16-byte chunks in the 128-byte row
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(ov[i + 0]) * inv, __uint_as_float(ov[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(ov[i + 4]) * inv, __uint_as_float(ov[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(ov[i + 6]) * inv, __uint_as_float(ov[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(prow_s + (((ch0 + (i >> 3)) ^ (row & 7)) << 4)) = w;
+          }
+        } else if (row < heads_here && a.n_split > 1) {
           float4* po = reinterpret_cast<float4*>(a.part_o + prow * kMlaDv + cta * kMlaDvHalf + c);
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
@@ -729,6 +766,16 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             *reinterpret_cast<uint4*>(orow + c + i) = w;
           }
         }
+      }
+    }
+    if (by_tma) {                                      // every thread of warps 0-7 comes here, whatever became of its waits
+      fence_async_smem();                              // the stores below read the panels through the async proxy
+      named_bar_sync(7, 256);
+      if (threadIdx.x == 0 && !*abort_flag) {
+#pragma unroll
+        for (int pn = 0; pn < 4; ++pn)                 // x in 4-byte units: 32 per 64-column panel
+          tma_store_2d(&tmap_o, kv_s + pn * kMlaQPanelBytes, (cta * 4 + pn) * 32, t * a.H + hg * 128);
+        bulk_commit_and_wait_read();                   // the panels have been read: the CTA may go
       }
     }
   }
@@ -780,11 +827,20 @@ int make_tmap_2d_bytes(CUtensorMap* m, const void* base, uint64_t rows, uint64_t
                        uint32_t box_bytes, uint32_t box_rows);
 
 template <bool FP8_PAGED>
-static int launch_mla(const void* q, const void* kv, const MlaArgs& a, cudaStream_t stream) {
-  if (a.T == 0 || a.H == 0) return DSA_OK;
-  CUtensorMap tq, tkv;
+static int launch_mla(const void* q, const void* kv, const MlaArgs& args, cudaStream_t stream) {
+  if (args.T == 0 || args.H == 0) return DSA_OK;
+  MlaArgs a = args;
+  CUtensorMap tq, tkv, to;
   int rc = make_tmap_2d_bytes(&tq, q, (uint64_t)a.T * a.H, kMlaDqk * 2, kMlaDqk * 2, 128, 128);
   if (rc) return rc;
+  // the output as [T*H rows x 1024 B], stored one [128 heads x 128 B] panel at a time -- when there is a full group of
+  // 128 heads, no split, and the tensor can be mapped (16-byte aligned)
+  a.tma_out = 0;
+  to = tq;
+  if (a.n_split == 1 && a.H >= 128 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
+    if ((rc = make_tmap_2d_bytes(&to, a.out, (uint64_t)a.T * a.H, kMlaDv * 2, kMlaDv * 2, 128, 128))) return rc;
+    a.tma_out = 1;
+  }
   // rows of the bf16 KV, one 64-dim panel (128 bytes) of one row per box: the shape tile::gather4 takes
   // (decode reads its cache with plain loads and only carries a copy of the Q map here)
   if (FP8_PAGED || a.S_kv == 0) tkv = tq;
@@ -793,7 +849,7 @@ static int launch_mla(const void* q, const void* kv, const MlaArgs& a, cudaStrea
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes) != cudaSuccess)
     return set_error(DSA_ERR_CUDA, "sparse_mla: cannot raise dynamic shared memory to %d", kMlaSmemBytes);
   const dim3 grid(2 * a.T * a.n_split, 1, (a.H + 127) / 128);
-  kern<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tq, tkv, a);
+  kern<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tq, tkv, to, a);
   if (a.n_split > 1) sparse_mla_combine_kernel<<<dim3(a.T, a.H), 128, 0, stream>>>(a);
   return check_launch("sparse_mla");
 }
