@@ -97,6 +97,16 @@ def _check_idx_out(out: Optional[torch.Tensor], T: int, k: int, device) -> torch
     return out
 
 
+def _check_attn_out(out: Optional[torch.Tensor], shape, device) -> torch.Tensor:
+    """The attention kernels write dense bf16 rows: a caller-supplied ``out`` must be exactly that."""
+    if out is None:
+        return torch.empty(shape, dtype=torch.bfloat16, device=device)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != tuple(shape) or not out.is_contiguous():
+        raise DsaError(f"out must be a contiguous bfloat16 {list(shape)} tensor, got {out.dtype} {tuple(out.shape)} "
+                       f"strides {tuple(out.stride())}")
+    return out
+
+
 def fp8_mqa_logits(q_fp8, kv, weights, ks, ke, clean_logits: bool = True,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Drop-in for ``deep_gemm.fp8_mqa_logits(q_fp8, (k_fp8, k_scale), w, ks, ke)``
@@ -251,8 +261,7 @@ def sparse_mla_prefill(q, kv, idx, scale: float, out: Optional[torch.Tensor] = N
         raise DsaError(f"bad shapes q {tuple(q.shape)} kv {tuple(kv.shape)} idx {tuple(idx.shape)}")
     q, kv, idx = q.contiguous(), kv.contiguous(), idx.contiguous()
     T, H, _ = q.shape
-    if out is None:
-        out = torch.empty(T, H, 512, dtype=torch.bfloat16, device=q.device)
+    out = _check_attn_out(out, (T, H, 512), q.device)
     lib = _lib.load()
     with torch.cuda.device(dev):
         check(lib.dsa_sparse_mla_prefill(_ptr(q), _ptr(kv), _ptr(idx), _ptr(out), T, H, kv.shape[0], idx.shape[1],
@@ -295,8 +304,7 @@ def sparse_mla_decode_paged(q, cache, block_table, idx, scale: float, max_ctx: O
     B, H, _ = q.shape
     if max_ctx is None:
         max_ctx = block_table.shape[1] * 64
-    if out is None:
-        out = torch.empty(B, H, 512, dtype=torch.bfloat16, device=q.device)
+    out = _check_attn_out(out, (B, H, 512), q.device)
     lib = _lib.load()
     if workspace is None:
         need = lib.dsa_sparse_mla_decode_workspace_bytes(B, H, idx.shape[1])

@@ -69,6 +69,18 @@ def test_large_scores_trigger_rescaling():
     check(out, O.sparse_mla(q.float(), kv.float(), idx, 0.2))
 
 
+def test_caller_supplied_out_must_be_dense_bf16_of_the_right_shape():
+    q, kv, idx = make(4, 128, 256, 64, seed=2)
+    q, kv, idx = q.cuda(), kv.cuda(), idx.cuda()
+    good = torch.empty(4, 128, 512, dtype=torch.bfloat16, device="cuda")
+    assert ops.sparse_mla_prefill(q, kv, idx, 0.05, out=good) is good
+    for bad in (torch.empty(4, 128, 512, dtype=torch.float16, device="cuda"),
+                torch.empty(4, 128, 256, dtype=torch.bfloat16, device="cuda"),
+                torch.empty(4, 128, 1024, dtype=torch.bfloat16, device="cuda")[:, :, ::2]):
+        with pytest.raises(ops.DsaError, match="out must be"):
+            ops.sparse_mla_prefill(q, kv, idx, 0.05, out=bad)
+
+
 def test_out_of_range_index_is_skipped_and_flagged():
     q, kv, idx = make(2, 128, 100, 64, seed=1, causal=False)
     bad = idx.clone()
