@@ -314,11 +314,11 @@ __device__ __forceinline__ void emit_unordered(TopkSmem& sm, const uint32_t (&ck
     if (feq & (1u << j)) o[pe++] = static_cast<int32_t>(~tkey[j]);
 }
 
-// Single pass over a long row, steered by a sample.  Returns false (for every thread of the block alike)
-// when the row has to take the two-pass path: geometry out of range, or the staged count missed [k, 4096].
-// Needs 16-byte aligned rows.
-__device__ __forceinline__ bool sampled_single_pass(TopkSmem& sm, const float* __restrict__ x, int lo, int hi, int k,
-                                                    int32_t* __restrict__ o) {
+// The threshold of the sampled pass: the key a few standard deviations below the sample's estimate of the k-th value.
+// Returns false (for every thread of the block alike) when the geometry of the row rules the sampled pass out.  The
+// result depends on the row alone, so every CTA that evaluates it for one row gets the same key.
+__device__ __forceinline__ bool sample_threshold(TopkSmem& sm, const float* __restrict__ x, int lo, int hi, int k,
+                                                 uint32_t& thr_out) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n = hi - lo;
   const int first = (lo + kVec - 1) & ~(kVec - 1);
@@ -384,17 +384,27 @@ __device__ __forceinline__ bool sampled_single_pass(TopkSmem& sm, const float* _
     digit_passes<kSamplePerThread>(sm, skey, svalid, prefix, pbits, need, 24);
     thr = prefix << 8;                                    // lower edge of the 24-bit bin of the sample's rf-th key
   }
+  thr_out = thr;
+  return true;
+}
 
-  // ---- one pass over the row: stage everything at or above thr ----------------------
+// One ordered pass over columns [lo, hi) of the row: stages everything whose key is at or above thr.
+// Returns the staged count, or 0xffffffff once it would exceed the capacity (uniform over the block).
+__device__ __forceinline__ uint32_t stage_above(TopkSmem& sm, const float* __restrict__ x, int lo, int hi, uint32_t thr) {
   const bool neg = (thr & 0x80000000u) == 0u;             // the threshold is a negative float
   const uint32_t tfb = neg ? ~thr : (thr ^ 0x80000000u);  // its bits as a float
-  const uint32_t staged = neg ? stage_row<true>(sm, x, lo, hi, tfb) : stage_row<false>(sm, x, lo, hi, tfb);
-  if (staged == 0xffffffffu || staged < (uint32_t)k) return false;   // missed [k, capacity]: two-pass path
+  return neg ? stage_row<true>(sm, x, lo, hi, tfb) : stage_row<false>(sm, x, lo, hi, tfb);
+}
 
-  // ---- exact k-th key among the candidates ---------------------------------------------
-  // Offsets d = key - thr are >= 0; when all are below 2^24 (floats within a few binades of the
-  // threshold) two 12-bit passes over d << 8 settle it, and their digits are mantissa bits, which
-  // spread over the histogram instead of piling onto a few exponent bins.
+// The exact k-th key among `staged` candidates (all with key >= thr, in any order) and the output.
+// Offsets d = key - thr are >= 0; when all are below 2^24 (floats within a few binades of the
+// threshold) two 12-bit passes over d << 8 settle it, and their digits are mantissa bits, which
+// spread over the histogram instead of piling onto a few exponent bins.
+__device__ __forceinline__ void select_among_staged(TopkSmem& sm, uint32_t staged, uint32_t thr, int k,
+                                                    int32_t* __restrict__ o) {
+  const int tid = threadIdx.x;
+  uint32_t prefix, need;
+  int pbits;
   uint32_t ck[kCandSPerThread];
   uint32_t valid = 0;
   int wide = 0;
@@ -419,14 +429,25 @@ __device__ __forceinline__ bool sampled_single_pass(TopkSmem& sm, const float* _
     kth_off = prefix;
   }
   emit_unordered<kCandSPerThread>(sm, ck, valid, kth_off, need, k, o);
+}
+
+// Single pass over a long row, steered by a sample.  Returns false (for every thread of the block alike)
+// when the row has to take the two-pass path: geometry out of range, or the staged count missed [k, 4096].
+// Needs 16-byte aligned rows.
+__device__ __forceinline__ bool sampled_single_pass(TopkSmem& sm, const float* __restrict__ x, int lo, int hi, int k,
+                                                    int32_t* __restrict__ o) {
+  uint32_t thr;
+  if (!sample_threshold(sm, x, lo, hi, k, thr)) return false;
+  const uint32_t staged = stage_above(sm, x, lo, hi, thr);
+  if (staged == 0xffffffffu || staged < (uint32_t)k) return false;   // missed [k, capacity]: two-pass path
+  select_among_staged(sm, staged, thr, k, o);
   return true;
 }
 
-__global__ void __launch_bounds__(kTopkThreads, 3)
-topk_select_kernel(const float* __restrict__ logits, int64_t ld, const int32_t* __restrict__ ks,
-                   const int32_t* __restrict__ ke, int T, int S, int k, int32_t* __restrict__ out, int sample) {
-  __shared__ TopkSmem sm;
-  const int row = blockIdx.x;
+// One row, one CTA: the whole selection.
+__device__ __forceinline__ void topk_row(TopkSmem& sm, const float* __restrict__ logits, int64_t ld,
+                                         const int32_t* __restrict__ ks, const int32_t* __restrict__ ke, int S, int k,
+                                         int32_t* __restrict__ out, int sample, int row) {
   const int tid = threadIdx.x;
   const int lo = ks ? max(ks[row], 0) : 0;
   const int hi = ke ? min(ke[row], S) : S;
@@ -582,10 +603,20 @@ topk_select_kernel(const float* __restrict__ logits, int64_t ld, const int32_t* 
   emit_candidates<kCandPerThread>(sm, ck, valid, prefix, need, n_above, k, o);
 }
 
+__global__ void __launch_bounds__(kTopkThreads, 3)
+topk_select_kernel(const float* __restrict__ logits, int64_t ld, const int32_t* __restrict__ ks,
+                   const int32_t* __restrict__ ke, int T, int S, int k, int32_t* __restrict__ out, int sample) {
+  __shared__ TopkSmem sm;
+  topk_row(sm, logits, ld, ks, ke, S, k, out, sample, blockIdx.x);
+}
+
 // sample = 0 forces the two-pass path on every row (the test hook that pits the two paths against each other)
 int topk_select_launch(const float* logits, int64_t ld, const int32_t* ks, const int32_t* ke, int T, int S, int k,
                        int32_t* out, int sample, cudaStream_t stream) {
   if (T == 0 || k == 0) return DSA_OK;
+  // (Tried for few long rows, i.e. decode: a cluster of four CTAs per row, each staging a quarter of the columns and
+  // CTA 0 collecting the candidates through distributed shared memory.  Same output, order included, and 22.2 us
+  // against 23.0 for 64 rows of 131072: the per-row sample / digit / emit phases, not the row pass, are the time.)
   topk_select_kernel<<<T, kTopkThreads, 0, stream>>>(logits, ld, ks, ke, T, S, k, out, sample);
   return check_launch("topk_select");
 }

@@ -159,6 +159,9 @@ def test_sampled_pass_equals_two_pass_on_adversarial_rows(S, k):
     assert torch.equal(a.sort(dim=1).values, b.sort(dim=1).values)
     _sets_equal_with_ties(x, a, k)
     T = x.shape[0]
+    # the output of a row does not depend on how many rows the call has
+    many = ops.topk_select(x.repeat(10, 1), k)
+    assert torch.equal(many[:T], a) and torch.equal(many[-T:], a)
     ks = torch.randint(0, S // 8, (T,), device=DEV, dtype=torch.int32, generator=g)
     ke = torch.randint(S - S // 8, S + 1, (T,), device=DEV, dtype=torch.int32, generator=g)
     a = ops.topk_select(x, k, ks, ke)
