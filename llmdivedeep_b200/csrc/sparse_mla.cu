@@ -269,7 +269,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   // tensor memory
   if (warp == 0) {
     if (lane < 21) {
-      const uint32_t count = (lane == 1 || lane == 4 || lane == 5) ? 256u           // q_moved, s_free, p_full: warps 0-7
+      const uint32_t count = (lane == 1 || lane == 4 || lane == 5) ? 8u             // q_moved, s_free, p_full: lane 0 of warps 0-7
                              : (lane == 7 || lane == 8) ? 8u                         // send_full: lane 0 of warps 0-7
                              : (lane == 11 || lane == 12) ? 8u                       // xchg_free: lane 0 of the peer's warps 0-7
                              : (lane >= 13 && lane <= 16) ? (FP8_PAGED ? uint32_t(kMlaGatherThreads) : uint32_t(kMlaGatherWarps))
@@ -383,19 +383,23 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
                       kd0 + uint64_t((4 * kMlaKPanelBytes) >> 4) + 2 * (rope_ks + u), idesc_qk, 1);
         umma_commit(s_full);
       };
-      // Whatever is ready goes first: P.V of the oldest block whose P is there, else the scores of the next block (its
-      // rows gathered, S read out by warps 0-7).  Blocking on one of the two while the other could run used to pace the
-      // kernel.  (Tried and dropped: chains first and P.V only inside a chain -- four P.V MMAs cost the pipe about 600
-      // cycles wherever they go.)
+      // Whatever is ready goes: the scores of the next block (its rows gathered, S read out by warps 0-7), else P.V of the
+      // oldest block whose P is there.  Blocking on one of the two while the other could run used to pace the kernel.
+      // (Tried and dropped: P.V only inside a chain -- four P.V MMAs cost the pipe about 600 cycles wherever they go.)
+      // The start of the next chain is what the block time hangs on, so the accumulator's release is polled first and
+      // the arrival of the gathered rows, once seen, is not polled again (a poll costs 100-150 cycles even on a barrier
+      // that is complete).
       uint32_t idle = 0;
+      bool rows_there = false;
       while (ok && pv < nblk) {
-        if (pv_ready()) {
-          pv_mmas(pv++);
-          idle = 0;
-        } else if (qk < nblk && mbar_try_wait(&kv_full[qk % NB], (qk / NB) & 1) &&
-                   (qk == 0 || mbar_try_wait(s_free, (qk - 1) & 1))) {
+        if (qk < nblk && !rows_there) rows_there = mbar_try_wait(&kv_full[qk % NB], (qk / NB) & 1);
+        if (rows_there && (qk == 0 || mbar_try_wait(s_free, (qk - 1) & 1))) {
           issue_qk(qk);
           ++qk;
+          rows_there = false;
+          idle = 0;
+        } else if (pv_ready()) {
+          pv_mmas(pv++);
           idle = 0;
         } else if (++idle > kFastSpins) {              // bounded like every other wait (dsa_common.cuh)
           if (*abort_flag) ok = false;
@@ -600,7 +604,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(q_moved);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_moved);             // one arrival per warp: 256 arrivals on one barrier queue up
     }
     cluster_wait();
     // Per iteration n: first half of the softmax of block n-1 (its peer tile arrived while this warp did other things:
@@ -655,7 +660,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tmem_ld32(t_row + kColS + 32 * half, sv);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(s_free);                           // the next block's scores may overwrite S now
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);            // the next block's scores may overwrite S now
         // the peer must have read block n-2, the last user of this stage (which also means that that copy is complete)
         if (n >= kMlaXStages) ok = __all_sync(0xffffffffu, mbar_wait(&xchg_free[st], ph ^ 1, abort_flag, a.status));
         if (!ok) break;
@@ -712,7 +718,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tmem_st16(t_row + kColP + 16 * half, pk);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(p_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
       }
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_final, 0, abort_flag, a.status));
