@@ -60,10 +60,15 @@ constexpr int kMlaXBytes = 128 * kMlaBlk * 2;      // one partial score tile, fp
 constexpr int kMlaXStages = 2;                     // exchange buffers (send and receive) per CTA
 constexpr int kMlaRing = 2;                        // row-id slots: read only by the gather warps, inside the call that staged them
 constexpr int kMlaMaskRing = 8;                    // validity masks (64 bits per block) for the softmax: >= blocks in flight
-constexpr int kMlaGatherWarps = 4;                 // the TMA unit, not the issuing warps, bounds the gather: more warps do not help
-constexpr int kMlaGatherThreads = kMlaGatherWarps * 32;
-constexpr int kMlaCopyWarp = 9 + kMlaGatherWarps;  // issues the copies of the partial score tiles
-constexpr int kMlaThreads = 288 + kMlaGatherThreads + 32;
+// Gather warps: four for prefill (the TMA unit, not the issuing warps, bounds that gather: more do not help), eight for
+// decode, where the warps convert the FP8 rows themselves and four of them take longer per block than the score chain.
+template <bool FP8_PAGED>
+struct MlaCfg {
+  static constexpr int kGatherWarps = FP8_PAGED ? 8 : 4;
+  static constexpr int kGatherThreads = kGatherWarps * 32;
+  static constexpr int kCopyWarp = 9 + kGatherWarps;          // issues the copies of the partial score tiles
+  static constexpr int kThreads = 288 + kGatherThreads + 32;
+};
 constexpr int kMlaBarBytes = 256;                  // mbarriers and a few words
 constexpr int kMlaPairBytes = 2 * 2 * 128 * 2;     // block maxima of the two key halves, double-buffered, bf16 (reused for the row sums, fp32)
 constexpr int kMlaSmemBytes = 1024 + kMlaBufs * kMlaKBytes + 2 * kMlaXStages * kMlaXBytes + kMlaBarBytes +
@@ -188,14 +193,15 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // e4m3 -> bf16 with the per-128 group scale, raw stage -> this CTA's four latent panels of a KV buffer.  Thread g of
-// kMlaGatherThreads; an empty slot was zero-filled (values and scales), so it converts to zeros.  (Tried and dropped:
+// GT gather threads; an empty slot was zero-filled (values and scales), so it converts to zeros.  (Tried and dropped:
 // decode's latent MMAs in fp16, so that e4m3 x scale is one conversion and one packed multiply per two values -- a third
 // of the instructions, and 9 % slower end to end: the conversion is not what paces the decode kernel.)
+template <int GT>
 __device__ __forceinline__ void convert_block(const uint8_t* stage, uint8_t* kv_s, int g, int cta) {
-  constexpr int kLat = kMlaBlk * 16 / kMlaGatherThreads;          // 16-value chunks per thread
+  constexpr int kLat = kMlaBlk * 16 / GT;          // 16-value chunks per thread
 #pragma unroll
   for (int u = 0; u < kLat; ++u) {
-    const int q = g + u * kMlaGatherThreads;
+    const int q = g + u * GT;
     const int r = q >> 4, cc = q & 15;              // row, chunk inside this CTA's 256 latent dims
     const uint4 raw = *reinterpret_cast<const uint4*>(stage + r * kRawRow + cc * 16);
     const float sc = *reinterpret_cast<const float*>(stage + r * kRawRow + kMlaDvHalf + (cta * 2 + (cc >> 3)) * 4);
@@ -216,12 +222,14 @@ __device__ __forceinline__ void convert_block(const uint8_t* stage, uint8_t* kv_
 }
 
 template <bool FP8_PAGED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MlaCfg<FP8_PAGED>::kThreads, 1)
 sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                   const __grid_constant__ CUtensorMap tmap_o, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int NB = FP8_PAGED ? kMlaBufs - 1 : kMlaBufs;      // KV buffers in use (decode: the fourth holds the raw stages)
+  constexpr int kMlaGatherWarps = MlaCfg<FP8_PAGED>::kGatherWarps, kMlaGatherThreads = MlaCfg<FP8_PAGED>::kGatherThreads;
+  constexpr int kMlaCopyWarp = MlaCfg<FP8_PAGED>::kCopyWarp, kMlaThreads = MlaCfg<FP8_PAGED>::kThreads;
   uint8_t* kv_s = smem;                                        // four buffers x five panels [64 keys x 128 B]
   uint8_t* send_s = kv_s + kMlaBufs * kMlaKBytes;              // [2] this CTA's partial score tiles
   uint8_t* recv_s = send_s + kMlaXStages * kMlaXBytes;         // [2] the peer's
@@ -505,9 +513,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (a.status) atomicCAS(a.status, kStatusOk, kStatusBadIndex);
         return -1;
       };
-      uint4 rope_e[2], rope_o[2];                      // rope chunks of the even / odd block in flight
+      constexpr int kRopePer = kMlaBlk * 4 / kMlaGatherThreads;      // 16-byte rope chunks per thread and block
+      uint4 rope_e[kRopePer], rope_o[kRopePer];        // rope chunks of the even / odd block in flight
       // request block b: stage its row ids (and the validity mask for the softmax), then issue the copies
-      auto fetch = [&](int b, int row, uint4 (&rope)[2]) {
+      auto fetch = [&](int b, int row, uint4 (&rope)[kRopePer]) {
         int* rows_s = ring + (b & 1) * kMlaBlk;
         if (g < kMlaBlk) {
           rows_s[g] = row;
@@ -529,7 +538,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             }
           }
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {                  // this CTA's two K-steps of the rope panel: 64 bytes per row
+          for (int u = 0; u < kRopePer; ++u) {           // this CTA's two K-steps of the rope panel: 64 bytes per row
             const int q = g + u * kMlaGatherThreads;
             const int rr = rows_s[q >> 2];
             rope[u] = make_uint4(0, 0, 0, 0);
@@ -549,7 +558,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         fetch(0, cache_row(p0, t0), rope_e);
         fetch(1, cache_row(p1, t1), rope_o);
       }
-      auto step = [&](int i, uint4 (&rope)[2]) -> bool {
+      auto step = [&](int i, uint4 (&rope)[kRopePer]) -> bool {
         const int kvb = i % NB;
         if (i == NB - 2) mbar_wait(q_moved, 0, abort_flag, a.status);    // buffers NB-2 and NB-1 held the Q panels
         if (i >= NB) mbar_wait(&kv_free[kvb], ((i / NB) - 1) & 1, abort_flag, a.status);
@@ -557,9 +566,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         // ... and everyone else's; every thread of the group takes the same way out of a failed wait
         if (named_bar_or(2, kMlaGatherThreads, *abort_flag != 0)) return false;
         uint8_t* dst = kv_s + kvb * kMlaKBytes;
-        convert_block(raw_s + (i & 1) * kRawStage, dst, g, cta);
+        convert_block<kMlaGatherThreads>(raw_s + (i & 1) * kRawStage, dst, g, cta);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kRopePer; ++u) {
           const int q = g + u * kMlaGatherThreads;
           const int r = q >> 2, c = cta * 4 + (q & 3);
           *reinterpret_cast<uint4*>(dst + 4 * kMlaKPanelBytes + r * 128 + ((c ^ (r & 7)) << 4)) = rope[u];
@@ -856,7 +865,7 @@ static int launch_mla(const void* q, const void* kv, const MlaArgs& args, cudaSt
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes) != cudaSuccess)
     return set_error(DSA_ERR_CUDA, "sparse_mla: cannot raise dynamic shared memory to %d", kMlaSmemBytes);
   const dim3 grid(2 * a.T * a.n_split, 1, (a.H + 127) / 128);
-  kern<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tq, tkv, to, a);
+  kern<<<grid, MlaCfg<FP8_PAGED>::kThreads, kMlaSmemBytes, stream>>>(tq, tkv, to, a);
   if (a.n_split > 1) sparse_mla_combine_kernel<<<dim3(a.T, a.H), 128, 0, stream>>>(a);
   return check_launch("sparse_mla");
 }
