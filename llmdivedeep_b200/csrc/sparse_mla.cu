@@ -228,6 +228,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int NB = FP8_PAGED ? kMlaBufs - 1 : kMlaBufs;      // KV buffers in use (decode: the fourth holds the raw stages)
+  // Whether a warp tells the peer that it has read a received tile before the peer may send into that stage again.  The
+  // order of a warp's work makes the acknowledgement redundant (see where the tile is written); prefill runs 1.3 % faster
+  // without it, decode -- at 96 registers per thread -- 4 % slower (the variant without it spills), so decode keeps it.
+  constexpr bool kAck = FP8_PAGED;
   constexpr int kMlaGatherWarps = MlaCfg<FP8_PAGED>::kGatherWarps, kMlaGatherThreads = MlaCfg<FP8_PAGED>::kGatherThreads;
   constexpr int kMlaCopyWarp = MlaCfg<FP8_PAGED>::kCopyWarp, kMlaThreads = MlaCfg<FP8_PAGED>::kThreads;
   uint8_t* kv_s = smem;                                        // four buffers x five panels [64 keys x 128 B]
@@ -358,7 +362,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       auto pick = [&](const uint64_t (&d)[kMlaBufs], int b) { return b == 0 ? d[0] : b == 1 ? d[1] : b == 2 ? d[2] : d[3]; };
       const uint32_t rope_ks = 2 * cta;              // this CTA's two K-steps of the rope panel
-      // P.V of block j: four MMAs (N = 256) and the commits that release the block's KV buffer, P and O
+      // P.V of block j: four MMAs (N = 256) and the commits that release the block's KV buffer, P and O.  They go as a
+      // group: alternated one by one with the MMAs of a score chain (so that each would run in the shadow of the chain's
+      // dependency latency) they cost far more -- 167 ms against 116 for the 128K prefill: every change between the two
+      // instruction shapes costs the pipe about 240 cycles, and a group has two of them.
       auto pv_mmas = [&](int j) {
         tc_fence_after();
         const uint64_t vd = pick(vdesc, j % NB);
@@ -642,8 +649,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             s[8 * c + 2 * k + 1] = x.y;
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive_remote_relaxed(peer_xchg_free + st * 8);      // the peer may send into this stage again
+        if constexpr (kAck) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive_remote_relaxed(peer_xchg_free + st * 8);    // the peer may send into this stage again
+        }
         const uint32_t used = masks[(j % kMlaMaskRing) * 2 + half];
         if (used != 0xffffffffu) {                       // empty slots (the tail of a short row, holes): warp-uniform
 #pragma unroll
@@ -661,7 +670,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       if (n < nblk) {
         // ---- partial scores of block n: tensor memory -> registers -> fp16 in send_s[stage]; the copy warp takes it from there
-        const int st = n & 1, ph = (n >> 1) & 1;
+        const int st = n & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(s_full, n & 1, abort_flag, a.status));
         if (!ok) break;
         tc_fence_after();
@@ -671,9 +680,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free);            // the next block's scores may overwrite S now
-        // the peer must have read block n-2, the last user of this stage (which also means that that copy is complete)
-        if (n >= kMlaXStages) ok = __all_sync(0xffffffffu, mbar_wait(&xchg_free[st], ph ^ 1, abort_flag, a.status));
-        if (!ok) break;
+        // The peer must have read block n-2, the last user of this stage (which also means that that copy is complete).
+        // That is already so without asking: this thread has seen the peer's block n-1 arrive (first half of the softmax
+        // above), the peer sent it only after all of its warps had written their parts, and each of them wrote its part
+        // after it had read this CTA's block n-2.  The same holds the other way round.
+        if constexpr (kAck) {
+          if (n >= kMlaXStages) ok = __all_sync(0xffffffffu, mbar_wait(&xchg_free[st], ((n >> 1) & 1) ^ 1, abort_flag, a.status));
+          if (!ok) break;
+        }
         uint8_t* send = send_s + st * kMlaXBytes;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
