@@ -363,9 +363,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       auto pick = [&](const uint64_t (&d)[kMlaBufs], int b) { return b == 0 ? d[0] : b == 1 ? d[1] : b == 2 ? d[2] : d[3]; };
       const uint32_t rope_ks = 2 * cta;              // this CTA's two K-steps of the rope panel
       // P.V of block j: four MMAs (N = 256) and the commits that release the block's KV buffer, P and O.  They go as a
-      // group: alternated one by one with the MMAs of a score chain (so that each would run in the shadow of the chain's
-      // dependency latency) they cost far more -- 167 ms against 116 for the 128K prefill: every change between the two
-      // instruction shapes costs the pipe about 240 cycles, and a group has two of them.
+      // group: alternated one by one with the MMAs of a score chain they cost far more (167 ms against 116 for the 128K
+      // prefill).  With A in tensor memory every MMA of this kernel costs its full ~137-cycle latency whether or not it
+      // depends on the one before (sixteen independent N = 64 MMAs in place of these four: +137 cycles each), so the
+      // block time is the number of MMA instructions, 18 + 4, times that.
       auto pv_mmas = [&](int j) {
         tc_fence_after();
         const uint64_t vd = pick(vdesc, j % NB);
