@@ -775,7 +775,7 @@ def main():
                 "ms_per_launch": ms_mla / max(1, len(pipe.chunks)), "flops_per_launch": flops_mla / max(1, len(pipe.chunks)),
                 # dram__bytes_read + dram__bytes_write of one ncu capture of the 512-token reduced case (125.3 MB + 49.0 MB),
                 # scaled by the tokens of one launch: q, idx and the output grow with the tokens, the latent KV does not
-                "traffic": (129.35e6 + 49.62e6) * (pipe.T_loc / max(1, len(pipe.chunks))) / 512,
+                "traffic": (129.19e6 + 49.12e6) * (pipe.T_loc / max(1, len(pipe.chunks))) / 512,
                 "traffic_source": "ncu capture of bench.py --case mla_prefill_small (512 tokens), scaled by tokens per launch",
                 "algorithmic_bytes": pipe.T_loc * MLA_HEADS * (576 + 512) * 2.0 + S * 1152.0 + pipe.T_loc * TOPK * 4.0,
                 "algorithmic_bytes_per_launch": (pipe.T_loc * (MLA_HEADS * (576 + 512) * 2.0 + TOPK * 4.0)) / max(1, len(pipe.chunks)) + S * 1152.0,
