@@ -39,7 +39,7 @@ constexpr int kPageTokens = 64;
 // work (64 accumulator columns) against the fixed cost of its barrier hand-offs: it moves 256 keys (four pages)
 // per tile, as two M=128 MMAs into adjacent accumulator columns.
 template <bool PAGED>
-__host__ __device__ constexpr int tile_keys() { return PAGED ? 2 * kTileKeys : kTileKeys; }
+__host__ __device__ constexpr int tile_keys() { return PAGED ? 4 * kTileKeys : kTileKeys; }
 
 struct IndexerArgs {
   const float* k_scale;      // [S] (contiguous) or [num_pages*64] (paged), one per key
@@ -79,7 +79,7 @@ struct IdxCfg {
   static constexpr int ACC_COLS = N * SUB;               // accumulator columns per stage
   static constexpr int K_TILE_BYTES = TILE_KEYS * D;
   static constexpr int Q_TILE_BYTES = N * D;
-  static constexpr int STAGES = PAGED ? 6 : 4;           // key tiles in flight (paged: 6 x 32 KB)
+  static constexpr int STAGES = PAGED ? 3 : 4;           // key tiles in flight (paged: 3 x 64 KB)
   static constexpr int TMEM_COLS = (2 * ACC_COLS < 32) ? 32 : 2 * ACC_COLS;
   static constexpr uint64_t SWZ = (D == 128) ? kSwz128 : kSwz64;
   static constexpr uint32_t SBO = 8 * D;                 // 8 rows of D bytes
@@ -88,7 +88,7 @@ struct IdxCfg {
   static constexpr int SPLIT = EPI / 2;                  // warpgroups sharing one accumulator stage
   static constexpr int COLS_PER_WG = N / SPLIT;
   static constexpr int CH = 16;                          // columns per TMEM load
-  static constexpr int AHEAD = PAGED ? 4 : 2;            // key tiles by which the k_scale prefetch runs ahead
+  static constexpr int AHEAD = 2;                        // key tiles by which the k_scale prefetch runs ahead
   static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * K_TILE_BYTES + 2 * QB * Q_TILE_BYTES +
                                     2 * QB * N * 4 + 2 * NTOK * 8 + 256 + (PAGED ? 4 * PAGES * kChunkTiles * 4 : 0) +
                                     AHEAD * SUB * EPI * 128 * 4;
